@@ -1,0 +1,66 @@
+// Status codes, error text and the device gate of the C ABI.
+#include "common.cuh"
+
+namespace xdk {
+
+static thread_local int g_last_cuda_error = 0;
+
+int note_launch(cudaError_t err) {
+  if (err == cudaSuccess) return XDK_OK;
+  g_last_cuda_error = static_cast<int>(err);
+  (void)cudaGetLastError();  // clear the sticky-free launch error so later calls start clean
+  return XDK_ERR_LAUNCH;
+}
+
+int require_sm100() {
+  static int verdict[64];  // 0 = unknown, 1 = ok, 2 = wrong architecture
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
+    (void)cudaGetLastError();
+    return XDK_ERR_ARCH;
+  }
+  if (dev < 64 && verdict[dev]) return verdict[dev] == 1 ? XDK_OK : XDK_ERR_ARCH;
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return XDK_ERR_ARCH;
+  }
+  if (dev < 64) verdict[dev] = major == 10 ? 1 : 2;
+  return major == 10 ? XDK_OK : XDK_ERR_ARCH;
+}
+
+}  // namespace xdk
+
+extern "C" {
+
+const char* xdk_strerror(int status) {
+  switch (status) {
+    case XDK_OK: return "ok";
+    case XDK_ERR_ARG: return "invalid argument (size, enum or null pointer)";
+    case XDK_ERR_ARCH: return "current CUDA device is not compute capability 10.x (B200, sm_100a)";
+    case XDK_ERR_LAUNCH: return "CUDA runtime refused the kernel launch (see xdk_last_cuda_error)";
+    case XDK_ERR_LIMIT: return "size beyond what this build supports";
+    default: return "unknown xdk status";
+  }
+}
+
+int xdk_abi_version(void) { return XDK_ABI_VERSION; }
+
+int xdk_last_cuda_error(void) { return xdk::g_last_cuda_error; }
+
+int xdk_device_supported(int device) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return XDK_ERR_ARCH;
+  }
+  if (device < 0 || device >= count) return XDK_ERR_ARG;
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return XDK_ERR_ARCH;
+  }
+  return major == 10 ? XDK_OK : XDK_ERR_ARCH;
+}
+
+}  // extern "C"

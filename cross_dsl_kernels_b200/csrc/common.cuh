@@ -1,0 +1,161 @@
+// Shared device/host helpers for the sm_100a decode kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/xdk_b200.h"
+
+namespace xdk {
+
+// ---- host side -------------------------------------------------------------------------------
+
+// Records the runtime's error for xdk_last_cuda_error() and maps it to a status.
+int note_launch(cudaError_t err);
+// XDK_OK when the device current to this thread is compute capability 10.x (cached per device).
+int require_sm100();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename... Args>
+inline int launch(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                  unsigned cluster_y, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  unsigned n_attr = 0;
+  if (cluster_y > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = cluster_y;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  return note_launch(cudaLaunchKernelEx(&cfg, kernel, args...));
+}
+
+// ---- device side -----------------------------------------------------------------------------
+
+struct alignas(16) U4 {
+  uint32_t x, y, z, w;
+};
+
+// 128-bit streaming load: read-only path, do not keep the line in L1 (each byte is used once).
+__device__ __forceinline__ U4 ld_stream16(const void* p) {
+  U4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// 128-bit load through the read-only cache for data every CTA re-reads (weights of a norm, tables).
+__device__ __forceinline__ U4 ld_cached16(const void* p) {
+  const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
+  return U4{t.x, t.y, t.z, t.w};
+}
+__device__ __forceinline__ float4 ld_stream_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float ld_stream_f1(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+// 128-bit streaming store (evict-first: the line is not read again by this kernel).
+__device__ __forceinline__ void st_stream16(void* p, const U4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  return v;
+}
+
+// Element <-> float conversions used by the kernels that are generic over storage type.
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static constexpr int kPerVec = 4;
+  __device__ static __forceinline__ float to_f32(float v) { return v; }
+  __device__ static __forceinline__ float from_f32(float v) { return v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static constexpr int kPerVec = 8;
+  __device__ static __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ static __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct Elem<__half> {
+  static constexpr int kPerVec = 8;
+  __device__ static __forceinline__ float to_f32(__half v) { return __half2float(v); }
+  __device__ static __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+
+// Unpack a 16-byte vector of T into floats and back (round-to-nearest-even on the way out).
+template <typename T>
+__device__ __forceinline__ void unpack16(const U4& v, float (&out)[Elem<T>::kPerVec]) {
+  const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int i = 0; i < Elem<T>::kPerVec; ++i) out[i] = Elem<T>::to_f32(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ U4 pack16(const float (&in)[Elem<T>::kPerVec]) {
+  U4 v;
+  T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+  for (int i = 0; i < Elem<T>::kPerVec; ++i) e[i] = Elem<T>::from_f32(in[i]);
+  return v;
+}
+
+// ---- mbarrier + bulk async copy (global -> this CTA's shared memory) ------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// Bounded wait: returns false if the phase did not complete within `spins` polls, so that a
+// lost copy can never hang the GPU; callers then skip the work and raise the error flag.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, unsigned spins = 1u << 22) {
+  const uint32_t addr = smem_u32(bar);
+  for (unsigned i = 0; i < spins; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// 1-D bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+}  // namespace xdk

@@ -1,0 +1,129 @@
+/*
+ * xdk_b200.h -- C ABI of the B200 (sm_100a) decode kernels.
+ *
+ * One shared library, libxdk_b200.so, replaces the four pybind11/ATen modules
+ * that upstream (AmanPandey28/cross_dsl_kernels) JIT-builds from
+ * csrc/{rmsnorm,gemv,rope_kv,w4a16}.  Every entry point
+ *   - takes plain device pointers the caller owns, sizes, and a CUDA stream
+ *     (a cudaStream_t passed as void*; NULL is the legacy default stream),
+ *   - launches asynchronously on that stream, never synchronises, never
+ *     allocates, keeps no state between calls, and may be stream-captured,
+ *   - validates sizes and pointers only (tensor-level checks -- dtype, rank,
+ *     contiguity, aliasing -- belong to the binding above it),
+ *   - returns XDK_OK or a negative xdk_status; it never throws.
+ * Paths below are upstream's, relative to its repository root.
+ */
+#ifndef XDK_B200_H_
+#define XDK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XDK_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define XDK_API __attribute__((visibility("default")))
+#else
+#define XDK_API
+#endif
+
+typedef enum xdk_status {
+  XDK_OK = 0,
+  XDK_ERR_ARG = -1,     /* a size, enum or NULL pointer is not acceptable          */
+  XDK_ERR_ARCH = -2,    /* the current device is not compute capability 10.x       */
+  XDK_ERR_LAUNCH = -3,  /* the CUDA runtime refused the launch; see xdk_last_cuda_error */
+  XDK_ERR_LIMIT = -4    /* a size exceeds what this build supports (stated per call) */
+} xdk_status;
+
+/* Storage type of activations for the ops that take more than one. */
+typedef enum xdk_dtype {
+  XDK_F32 = 0,
+  XDK_BF16 = 1,
+  XDK_F16 = 2 /* extension: upstream's CUDA kernels take FP32/BF16 only */
+} xdk_dtype;
+
+/* Human-readable text for a status code (static storage). */
+XDK_API const char* xdk_strerror(int status);
+/* XDK_ABI_VERSION the library was built with. */
+XDK_API int xdk_abi_version(void);
+/* cudaError_t (as int) of the most recent failed launch on this host thread, 0 if none. */
+XDK_API int xdk_last_cuda_error(void);
+/* XDK_OK when `device` exists and is compute capability 10.x, else XDK_ERR_ARCH/ARG. */
+XDK_API int xdk_device_supported(int device);
+
+/*
+ * Fused residual RMSNorm:  r = x + residual (FP32);  y = r * rsqrt(mean(r^2) + eps) * weight;
+ * writes y (rounded to dtype) and residual_out = r (rounded to dtype).  The
+ * UNROUNDED sum is normalised.  x, residual, y, residual_out: [rows, hidden]
+ * contiguous; weight: [hidden]; all of `dtype`.  Any alignment and any
+ * hidden >= 1 are accepted (16-byte aligned pointers with hidden a multiple of
+ * 16 bytes take the vector path).  Outputs must not alias inputs.
+ * Replaces fused_residual_rmsnorm (csrc/rmsnorm/rmsnorm_ext.cpp:10-35) ->
+ * crossdsl_fused_residual_rmsnorm_cuda (csrc/rmsnorm/rmsnorm_kernel.cu:364-371).
+ */
+XDK_API int xdk_rmsnorm(const void* x, const void* residual, const void* weight, void* y, void* residual_out,
+                int64_t rows, int64_t hidden, float eps, int dtype, void* stream);
+
+/*
+ * FP32 decode projection  y[M,N] = x[M,K] * W (+ bias[N]).
+ * W is [K,N] row-major (weight_is_nk = 0) or [N,K] row-major (weight_is_nk = 1).
+ * split_k in {1,2,4,8}: K is cut into split_k contiguous ranges (length
+ * ceil(K/split_k) rounded up to a multiple of 32) that are reduced in a fixed
+ * order inside one launch (thread-block cluster, distributed shared memory);
+ * bias is added once, after the reduction.  split_k = 0 lets the library pick.
+ * Results are deterministic for a given (shape, split_k).  FP32 FMA
+ * accumulation, no TF32.  bias may be NULL.  M, K, N >= 1; M > 16 is processed
+ * in row tiles of 16 (the weight stream repeats per tile).
+ * Replaces decode_gemv / decode_gemv_warp / decode_gemv_rows
+ * (csrc/gemv/gemv_ext.cpp:57-85), decode_gemv_simt_{warp,rows} and
+ * decode_gemm_tiled (csrc/gemv/gemv_simt_ext.cpp:49-83); split-K semantics as
+ * src/crossdsl_kernels/triton/gemv_rows.py:47-146.
+ */
+XDK_API int xdk_gemv_f32(const float* x, const float* w, const float* bias, float* y,
+                 int64_t m, int64_t k, int64_t n, int weight_is_nk, int split_k, void* stream);
+
+/*
+ * Fused rotary embedding + paged K/V cache append, one launch.
+ * q [tokens,q_heads,head_dim], k,v [tokens,kv_heads,head_dim], q_out like q;
+ * cos,sin FP32 [*, cos_width] (columns [0, rope_dim/2) are read, row = position);
+ * positions, sequence_ids int64 [tokens]; page_table int64 [*, max_pages_per_seq];
+ * caches [pages,page_size,kv_heads,head_dim] (cache_is_hnd = 0) or
+ * [pages,kv_heads,page_size,head_dim] (cache_is_hnd = 1), same dtype as q/k/v.
+ * Token t goes to physical page page_table[sequence_ids[t]][positions[t] / page_size],
+ * in-page offset positions[t] % page_size.  The first rope_dim dims of each Q
+ * and K head are rotated (pairs (i, i+rope_dim/2), or (2i, 2i+1) when
+ * interleaved) with separately rounded FP32 multiplies and add/subtract -- no
+ * fused multiply-add -- then rounded to dtype, so results are bit-identical to
+ * the PyTorch reference; other dims and V are copied.  Index VALUES are not
+ * checked on the device (the caller validates them at set-up); all other cache
+ * slots are left untouched.
+ * Replaces rope_gqa_paged_kv_append (csrc/rope_kv/rope_kv_ext.cpp:28-131) ->
+ * crossdsl_rope_gqa_paged_kv_append_cuda (csrc/rope_kv/rope_kv_kernel.cu:200-275).
+ */
+XDK_API int xdk_rope_kv_append(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                       const int64_t* positions, const int64_t* page_table, const int64_t* sequence_ids,
+                       void* q_out, void* k_cache, void* v_cache,
+                       int64_t tokens, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                       int64_t cos_width, int64_t max_pages_per_seq, int64_t page_size, int64_t rope_dim,
+                       int interleaved, int cache_is_hnd, int dtype, void* stream);
+
+/*
+ * W4A16 projection  y[M,N] = half( x[M,K] * W^T (+ bias[N]) ), FP32 accumulation.
+ * packed: uint8 [N, ceil(K/2)], two 4-bit codes per byte, even k in the low
+ * nibble, value = code - 8; scales: FP16 [N, ceil(K/group_size)],
+ * group_size in {32,64,128,256}; W[n][k] = half(float(value) * float(scale)),
+ * that rounding included.  x, bias (nullable), y are FP16.  1 <= M <= 16.
+ * Replaces linear_out (csrc/w4a16/w4a16_ext.cpp:7-39) -> w4a16_launch
+ * (csrc/w4a16/w4a16_kernel.cu:45-63).
+ */
+XDK_API int xdk_w4a16(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
+              int64_t m, int64_t k, int64_t n, int group_size, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XDK_B200_H_ */
