@@ -39,6 +39,7 @@ struct RopeShape {
   int q_heads, kv_heads, head_dim, rope_dim;
   int cos_width, page_size;
   int64_t max_pages;
+  int64_t q_stride, k_stride, v_stride;  // elements between consecutive tokens of q, k, v
   int hnd;
 };
 
@@ -93,15 +94,15 @@ rope_append_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
 
   // ---- payload loads first (independent of every index)
   const T* src = kind == 0 ? q : (kind == 1 ? k : v);
-  const int heads_here = kind == 0 ? s.q_heads : s.kv_heads;
-  const int64_t src_row = (static_cast<int64_t>(token) * heads_here + head) * s.head_dim;
+  const int64_t stride = kind == 0 ? s.q_stride : (kind == 1 ? s.k_stride : s.v_stride);
+  const int64_t src_row = static_cast<int64_t>(token) * stride + static_cast<int64_t>(head) * s.head_dim;
   Chunk<T, W> a, b;
   a.load(src + src_row + static_cast<int64_t>(first) * W);
   if (second >= 0) b.load(src + src_row + static_cast<int64_t>(second) * W);
 
   // ---- dependent index chain
   const int64_t pos = __ldg(positions + token);
-  int64_t dst_row = src_row;  // Q: same place in q_out
+  int64_t dst_row = (static_cast<int64_t>(token) * s.q_heads + head) * s.head_dim;  // Q: contiguous q_out
   T* dst = q_out;
   if (kind != 0) {
     const int64_t seq = __ldg(sequence_ids + token);
@@ -190,12 +191,12 @@ rope_append_scalar_interleaved_kernel(const T* __restrict__ q, const T* __restri
     kind = 2;
   }
   const T* src = kind == 0 ? q : (kind == 1 ? k : v);
-  const int heads_here = kind == 0 ? s.q_heads : s.kv_heads;
-  const int64_t src_row = (static_cast<int64_t>(token) * heads_here + head) * s.head_dim;
+  const int64_t stride = kind == 0 ? s.q_stride : (kind == 1 ? s.k_stride : s.v_stride);
+  const int64_t src_row = static_cast<int64_t>(token) * stride + static_cast<int64_t>(head) * s.head_dim;
   float lo = Elem<T>::to_f32(src[src_row + d0]);
   float hi = d1 >= 0 ? Elem<T>::to_f32(src[src_row + d1]) : 0.0f;
   const int64_t pos = __ldg(positions + token);
-  int64_t dst_row = src_row;
+  int64_t dst_row = (static_cast<int64_t>(token) * s.q_heads + head) * s.head_dim;
   T* dst = q_out;
   if (kind != 0) {
     const int64_t seq = __ldg(sequence_ids + token);
@@ -225,7 +226,8 @@ int dispatch_all(const void* q, const void* k, const void* v, const float* cos, 
   const bool aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(q_out) && aligned16(k_cache) &&
                        aligned16(v_cache);
   // Vector path: whole 16-byte chunks, and rotation partners that fall on chunk boundaries.
-  const bool vec = aligned && s.head_dim % E == 0 && (interleaved ? s.rope_dim % E == 0 : (s.rope_dim / 2) % E == 0);
+  const bool vec = aligned && s.head_dim % E == 0 && s.q_stride % E == 0 && s.k_stride % E == 0 &&
+                   s.v_stride % E == 0 && (interleaved ? s.rope_dim % E == 0 : (s.rope_dim / 2) % E == 0);
 #define XDK_ROPE(WW, IL)                                                                                          \
   return launch_rope<T, WW, IL>(q, k, v, cos, sin, positions, page_table, sequence_ids, q_out, k_cache, v_cache, \
                                 tokens, s, stream)
@@ -253,7 +255,8 @@ extern "C" int xdk_rope_kv_append(const void* q, const void* k, const void* v, c
                                   const int64_t* positions, const int64_t* page_table, const int64_t* sequence_ids,
                                   void* q_out, void* k_cache, void* v_cache, int64_t tokens, int64_t q_heads,
                                   int64_t kv_heads, int64_t head_dim, int64_t cos_width, int64_t max_pages_per_seq,
-                                  int64_t page_size, int64_t rope_dim, int interleaved, int cache_is_hnd, int dtype,
+                                  int64_t page_size, int64_t rope_dim, int64_t q_token_stride, int64_t k_token_stride,
+                                  int64_t v_token_stride, int interleaved, int cache_is_hnd, int dtype,
                                   void* stream) {
   if (!q || !k || !v || !cos || !sin || !positions || !page_table || !sequence_ids || !q_out || !k_cache || !v_cache)
     return XDK_ERR_ARG;
@@ -261,6 +264,9 @@ extern "C" int xdk_rope_kv_append(const void* q, const void* k, const void* v, c
     return XDK_ERR_ARG;
   if (q_heads % kv_heads != 0) return XDK_ERR_ARG;
   if (rope_dim <= 0 || rope_dim % 2 != 0 || rope_dim > head_dim || cos_width < rope_dim / 2) return XDK_ERR_ARG;
+  if (q_token_stride < q_heads * head_dim || k_token_stride < kv_heads * head_dim ||
+      v_token_stride < kv_heads * head_dim)
+    return XDK_ERR_ARG;
   const int64_t int_max = 2147483647LL;
   if (tokens > int_max || q_heads > 65535 || kv_heads > 65535 || head_dim > 65536 || cos_width > int_max ||
       page_size > int_max)
@@ -274,6 +280,7 @@ extern "C" int xdk_rope_kv_append(const void* q, const void* k, const void* v, c
   s.cos_width = static_cast<int>(cos_width);
   s.page_size = static_cast<int>(page_size);
   s.max_pages = max_pages_per_seq;
+  s.q_stride = q_token_stride, s.k_stride = k_token_stride, s.v_stride = v_token_stride;
   s.hnd = cache_is_hnd ? 1 : 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool il = interleaved != 0;

@@ -111,8 +111,12 @@ def rope_gqa_paged_kv_append(q, k, v, cos, sin, positions, page_table, sequence_
                           ("sequence_ids", sequence_ids, torch.int64)):
         _need(t.is_cuda and t.device == q.device, f"{name} must be on the same CUDA device as q")
         _need(t.dtype == want, f"{name} has an unexpected dtype")
-        _need(t.is_contiguous(), f"{name} must be contiguous")
-    _need(q.is_contiguous(), "q must be contiguous")
+        _need(name in ("k", "v") or t.is_contiguous(), f"{name} must be contiguous")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        # contiguous, or a column slice of a wider row-major matrix (fused QKV output):
+        # heads and dims dense, tokens a fixed number of elements apart
+        dense = t.dim() == 3 and t.stride(2) == 1 and t.stride(1) == t.shape[2] and t.stride(0) >= t.shape[1] * t.shape[2]
+        _need(t.is_contiguous() or dense, f"{name} must be contiguous or a column slice of a row-major matrix")
     _need(q.dim() == 3 and k.dim() == 3 and v.dim() == 3, "q, k, v must be [tokens, heads, head_dim]")
     _need(cos.dim() == 2 and sin.dim() == 2, "cos and sin must be [max_position, >= rope_dim / 2]")
     _need(positions.dim() == 1 and sequence_ids.dim() == 1, "positions and sequence_ids must be vectors")
@@ -138,11 +142,12 @@ def rope_gqa_paged_kv_append(q, k, v, cos, sin, positions, page_table, sequence_
     _need(tuple(k_cache.shape[1:]) == want, f"{layout} cache dimensions must be (pages, {want})")
     validate_cache_storage((q, k, v, cos, sin, positions, page_table, sequence_ids), k_cache, v_cache)
     with torch.cuda.device(q.device):
-        q_out = torch.empty_like(q)
+        q_out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         status = _native.lib().xdk_rope_kv_append(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(),
             page_table.data_ptr(), sequence_ids.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
             tokens, q_heads, kv_heads, head_dim, cos.shape[1], page_table.shape[1], page_size, rope_dim,
-            int(bool(interleaved)), int(layout == "HND"), _native.dtype_code(dtype), _native.stream_ptr(q.device))
+            q.stride(0) if tokens > 1 else q_heads * head_dim, k.stride(0) if tokens > 1 else kv_heads * head_dim,
+            v.stride(0) if tokens > 1 else kv_heads * head_dim, int(bool(interleaved)), int(layout == "HND"), _native.dtype_code(dtype), _native.stream_ptr(q.device))
     _native.check(status, "xdk_rope_kv_append")
     return q_out

@@ -1,0 +1,131 @@
+"""CUDA-graph timing: the "per-call median" metric.
+
+A graph holding ``len(calls)`` back-to-back launches is replayed several times;
+each replay is timed with CUDA events on the capturing stream and the median
+replay time is divided by the number of calls (the method of upstream's
+benchmarks/common.py:129-153).  Callers pass one closure per call so that
+consecutive calls can use different buffer sets: when the sets together exceed
+the 126 MB L2, every call streams from HBM instead of hitting lines the
+previous call left behind.
+"""
+
+from __future__ import annotations
+
+import statistics
+import subprocess
+import threading
+from typing import Callable, Sequence
+
+import torch
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def rotation_for(working_set_bytes: int, target_bytes: int = 3 * L2_BYTES, cap: int = 64) -> int:
+    """How many distinct buffer sets make consecutive calls miss L2."""
+    return max(1, min(cap, -(-target_bytes // max(1, working_set_bytes))))
+
+
+def capture(calls: Sequence[Callable[[], object]], stream: torch.cuda.Stream | None = None) -> torch.cuda.CUDAGraph:
+    stream = stream or torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for fn in calls:  # warm-up outside capture: loads modules, sizes allocator pools
+            fn()
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for fn in calls:
+            fn()
+    return graph
+
+
+def replay_times_ms(graph: torch.cuda.CUDAGraph, replays: int = 20, warmup: int = 3) -> list[float]:
+    for _ in range(warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(replays):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        end.synchronize()
+        times.append(start.elapsed_time(end))
+    return times
+
+
+def graph_median_us(calls: Sequence[Callable[[], object]], replays: int = 20, warmup: int = 3) -> dict:
+    graph = capture(calls)
+    times = replay_times_ms(graph, replays, warmup)
+    per_call = [t * 1e3 / len(calls) for t in times]
+    ordered = sorted(per_call)
+    return {
+        "median_us": statistics.median(per_call),
+        "p10_us": ordered[max(0, int(0.1 * len(ordered)) - 0)],
+        "p90_us": ordered[min(len(ordered) - 1, int(0.9 * len(ordered)))],
+        "min_us": ordered[0],
+        "calls_per_graph": len(calls),
+        "replays": replays,
+    }
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int = 0, period_ms: int = 100):
+        self.cmd = ["nvidia-smi", f"--id={device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                    "-lms", str(period_ms)]
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return self
+
+        def pump():
+            for line in self.proc.stdout:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) == 7:
+                    self.rows.append(parts)
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=5)
+
+    def summary(self) -> dict:
+        clocks, max_clock, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for row in self.rows:
+            try:
+                clocks.append(float(row[0]))
+                max_clock = float(row[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, row[3:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max_clock,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }

@@ -88,7 +88,9 @@ XDK_API int xdk_gemv_f32(const float* x, const float* w, const float* bias, floa
 
 /*
  * Fused rotary embedding + paged K/V cache append, one launch.
- * q [tokens,q_heads,head_dim], k,v [tokens,kv_heads,head_dim], q_out like q;
+ * q [tokens,q_heads,head_dim], k,v [tokens,kv_heads,head_dim]; consecutive tokens of q, k, v are
+ * {q,k,v}_token_stride elements apart (heads*head_dim when contiguous; larger when the three are
+ * column slices of one fused QKV projection output); q_out is contiguous [tokens,q_heads,head_dim];
  * cos,sin FP32 [*, cos_width] (columns [0, rope_dim/2) are read, row = position);
  * positions, sequence_ids int64 [tokens]; page_table int64 [*, max_pages_per_seq];
  * caches [pages,page_size,kv_heads,head_dim] (cache_is_hnd = 0) or
@@ -109,6 +111,7 @@ XDK_API int xdk_rope_kv_append(const void* q, const void* k, const void* v, cons
                        void* q_out, void* k_cache, void* v_cache,
                        int64_t tokens, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                        int64_t cos_width, int64_t max_pages_per_seq, int64_t page_size, int64_t rope_dim,
+                       int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
                        int interleaved, int cache_is_hnd, int dtype, void* stream);
 
 /*

@@ -1,0 +1,130 @@
+"""GPU parity of the W4A16 projection.  Gates: |err| <= 0.002 + 0.002 |ref| and
+rel-L2 <= 1e-3 against the FP64 product with the FP16-rounded dequantised
+weights (upstream benchmarks/w4a16_benchmark.py:33-57), and relative error
+<= 2e-3 against the dequantised FP32 matmul."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import load_golden, rel_l2
+from cross_dsl_kernels_b200 import quantization as qz
+from oracle import int4
+
+pytestmark = pytest.mark.gpu
+
+
+def gate(y, x, packed, scales, bias, group):
+    ref = int4.w4a16_projection(x, packed, scales, bias, group_size=group)
+    err = (y.cpu().double() - ref.double()).abs()
+    assert bool((err <= 0.002 + 0.002 * ref.double().abs()).all()), float(err.max())
+    assert rel_l2(y.cpu(), ref) <= 1e-3
+    dense = int4.w4a16_projection_f32(x, packed, scales, bias, group_size=group)
+    assert rel_l2(y.cpu(), dense) <= 2e-3
+    return rel_l2(y.cpu(), ref)
+
+
+def make(m, k, n, group, bias, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    codes = torch.randint(0, 16, (n, k), generator=g)
+    packed = qz.pack_int4((codes - 8).to(torch.int8))
+    scales = (0.005 + 0.015 * torch.rand(n, -(-k // group), generator=g)).half()
+    x = torch.randn(m, k, generator=g).half()
+    b = (0.02 * torch.randn(n, generator=g)).half() if bias else None
+    return x, packed, scales, b
+
+
+def test_golden_cases():
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    for case in load_golden("w4a16"):
+        if "quantize_input" in case:
+            continue
+        b = case["bias"].cuda() if case["bias"] is not None else None
+        y = w4a16_linear(case["x"].cuda(), case["packed"].cuda(), case["scales"].cuda(), b, group_size=case["group_size"])
+        err = (y.cpu().double() - case["y"].double()).abs()
+        assert bool((err <= 0.002 + 0.002 * case["y"].double().abs()).all())
+        assert rel_l2(y.cpu(), case["y"]) <= 1e-3
+
+
+@pytest.mark.parametrize("m", [1, 16])
+@pytest.mark.parametrize("n", [4096, 14336])
+def test_baseline_shapes(m, n):
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    x, packed, scales, _ = make(m, 4096, n, 128, False)
+    y = w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), None, group_size=128)
+    worst = gate(y, x, packed, scales, None, 128)
+    assert worst <= 3e-4, "FP32 accumulation should land far inside the gate"
+    out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    y2 = w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), None, group_size=128, out=out)
+    assert y2 is out and torch.equal(y2, y)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 9, 16])
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
+def test_every_m_and_group(m, group):
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    x, packed, scales, b = make(m, 1024, 200, group, True, seed=m * 10 + group)
+    y = w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), b.cuda(), group_size=group)
+    gate(y, x, packed, scales, b, group)
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 33, 5), (2, 1, 1), (3, 257, 9), (16, 31, 7), (4, 96, 17), (16, 6144, 64),
+                                   (1, 128, 8), (16, 4096, 6144), (5, 2048, 1001)])
+def test_odd_shapes(m, k, n):
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    x, packed, scales, b = make(m, k, n, 32, True, seed=k)
+    y = w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), b.cuda(), group_size=32)
+    gate(y, x, packed, scales, b, 32)
+
+
+def test_all_sixteen_codes_with_exact_scales():
+    """Every code value with power-of-two scales: products and sums are exact, so
+    the result must equal the oracle bit for bit (upstream scripts/verify_w4a16.py:30-43)."""
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    n, k = 32, 256
+    codes = (torch.arange(n * k).reshape(n, k) % 16).to(torch.int8) - 8
+    packed = qz.pack_int4(codes)
+    scales = torch.tensor([0.5, 0.25]).repeat(n, 1).half()
+    x = (torch.arange(k) % 5 - 2).float().repeat(3, 1).half()
+    y = w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), None, group_size=128)
+    assert torch.equal(y.cpu(), int4.w4a16_projection(x, packed, scales, None, group_size=128))
+
+
+def test_graph_replay_follows_changed_inputs():
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    x, packed, scales, b = make(16, 1024, 512, 128, True)
+    xd, pd, sd, bd = x.cuda(), packed.cuda(), scales.cuda(), b.cuda()
+    out = torch.empty(16, 512, dtype=torch.float16, device="cuda")
+    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        w4a16_linear(xd, pd, sd, bd, out=out)
+    side.synchronize()
+    gate(out, x, packed, scales, b, 128)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        w4a16_linear(xd, pd, sd, bd, out=out)
+    x2 = torch.randn(16, 1024, generator=torch.Generator().manual_seed(3)).half()
+    xd.copy_(x2); out.fill_(float("nan"))
+    graph.replay(); torch.cuda.synchronize()
+    gate(out, x2, packed, scales, b, 128)
+
+
+def test_rejections():
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    x, packed, scales, b = (t.cuda() for t in make(2, 64, 8, 32, True))
+    bad = [
+        lambda: w4a16_linear(x, packed, scales, b, group_size=48),
+        lambda: w4a16_linear(x.float(), packed, scales, b, group_size=32),
+        lambda: w4a16_linear(x, packed[:, :16].contiguous(), scales, b, group_size=32),
+        lambda: w4a16_linear(x, packed, scales[:, :1].contiguous(), b, group_size=32),
+        lambda: w4a16_linear(x, packed, scales, b[:4], group_size=32),
+        lambda: w4a16_linear(x, packed, scales, b, group_size=32, out=torch.empty(2, 9, dtype=torch.float16, device="cuda")),
+        lambda: w4a16_linear(x, packed, scales, b, group_size=32, out=x.view(-1)[:16].view(2, 8)),
+        lambda: w4a16_linear(torch.zeros(17, 64, dtype=torch.float16, device="cuda"), packed, scales, b, group_size=32),
+        lambda: w4a16_linear(x, packed, scales, b, group_size=32, rows_per_block=3),
+        lambda: w4a16_linear(x.cpu(), packed, scales, b, group_size=32),
+    ]
+    for call in bad:
+        with pytest.raises((ValueError, RuntimeError)):
+            call()
