@@ -133,22 +133,33 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-// Bounded wait: returns false if the phase did not complete within `spins` polls, so that a
-// lost copy can never hang the GPU; callers then skip the work and raise the error flag.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, unsigned spins = 1u << 22) {
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: returns false if the phase did not complete within `budget_ns` of wall time
+// (default 20 ms, far beyond any legitimate wait inside these microsecond-scale kernels), so a
+// lost copy or a protocol bug can never hang the GPU; callers then skip the work and raise a flag.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, uint64_t budget_ns = 20000000ull) {
   const uint32_t addr = smem_u32(bar);
-  for (unsigned i = 0; i < spins; ++i) {
+  uint64_t t0 = 0;
+  for (unsigned i = 0;; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
+    if ((i & 15u) == 15u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) return false;
+    }
   }
-  return false;
 }
 // 1-D bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes, uint64_t* bar) {

@@ -7,7 +7,23 @@
 // 1024 + code exactly), turned into code - 8 exactly, and multiplied by the FP16 scale with one
 // FP16 rounding -- bit-identical to the format's definition half(float(q) * float(scale)), since
 // that FP32 product is exact.  Products with x accumulate in FP32.
+//
+// Two compute paths share the unpack:
+//   * M <= 2: SIMT.  Lanes stride over the packed row, weights feed mixed-precision FMAs
+//     (FP16 operands, FP32 accumulator) and a warp shuffle finishes each column.
+//   * 3 <= M <= 16: tensor cores.  The op is then a real [16 x K] x [K x N] contraction: x is padded to
+//     16 rows and the dequantised weights go straight from registers into mma.m16n8k16 B fragments
+//     (FP32 accumulators).  The k order inside a fragment is free as long as A uses the same order, so
+//     x is stored in shared memory pre-permuted to the order the unpack produces and no weight ever
+//     moves between lanes.
+// Split-K slices of one column strip form a thread-block cluster and are summed in slice order
+// through distributed shared memory (one launch, no scratch, deterministic).
+#include <cooperative_groups.h>
+#include <cuda.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace xdk {
 namespace {
@@ -64,7 +80,7 @@ __device__ __forceinline__ int swz(int unit) { return unit ^ ((unit >> 3) & 3); 
 template <int MT, int CW>
 __global__ void __launch_bounds__(kThreads)
 w4a16_simt_kernel(W4Args a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   U4* xs = reinterpret_cast<U4*>(smem_raw);  // [MT][K/8] swizzled 16-byte units
   const int units = a.k / 8;
   for (int i = threadIdx.x; i < MT * units; i += kThreads) {
@@ -148,6 +164,395 @@ w4a16_simt_kernel(W4Args a) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tensor-core building blocks.  A warp works on blocks of 8 columns in steps of 128 k: in a step
+// lane (g = lane/4, j = lane%4) holds the 16 bytes with k in [32j, 32j+32) of column g of the block.
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Physical position of 16-byte unit `unit` of x row `row`: the XOR spreads the eight units a
+// quarter-warp reads in one shared-memory phase (2 rows x 4 lanes) over all eight bank groups.
+__device__ __forceinline__ int xunit(int unit, int row) { return unit ^ ((((unit >> 3) & 1) << 1) | (row & 1)); }
+
+// ------------------------------------------------------------------------------------------------
+// Streaming tensor-core path (the one used for 3 <= M <= 16 when K % 128 == 0).
+//
+// One persistent CTA per SM.  The N/8 column blocks are dealt out evenly to clusters of S CTAs
+// (S = split-K factor, 1/2/4); inside a cluster CTA r takes the K chunks r, r+S, ... of 1024 k, and
+// inside a CTA warp w takes blocks w, w+8, ...  A (chunk, block) tile is 8 column rows of 512 packed
+// bytes plus their scales.  Every warp runs its own software pipeline: an elected lane keeps the TMA
+// box copies (one op for the weights, one for the scales) of the warp's next three tiles in flight
+// into a private four-slot shared-memory ring, completing on per-slot mbarriers, while the warp
+// unpacks the current tile in registers and feeds mma.m16n8k16.  (A warp can only keep a handful
+// of ordinary load instructions in flight; one TMA op moves a whole 4 KB tile.)  x for the current chunk sits in shared memory, pre-permuted and swizzled
+// as in the path above and double-buffered across chunks.  Partial sums of the S CTAs meet through
+// distributed shared memory in rank order.
+constexpr int kStreamWarps = 8;
+constexpr int kStreamThreads = kStreamWarps * 32;
+constexpr int kChunkK = 1024;                       // k per chunk
+constexpr int kRowStride = kChunkK / 2;             // a tile is a dense TMA box: 8 column rows x 512 B
+constexpr int kSlotBytes = 8 * kRowStride + 512;    // + up to 8 x 64 B of scales (dense box, 8 rows)
+// ring slots per warp: all but one hold tiles in flight; 16 staged x rows leave room for 3, 8 rows for 4
+template <bool ROWS16> struct StreamDepth { static constexpr int value = ROWS16 ? 3 : 4; };
+constexpr int kMaxNB = 8;                           // column blocks per warp per pass
+
+__device__ unsigned int g_w4_fault;  // set when a bounded wait gives up
+
+struct StreamPlan {
+  int clusters;        // number of clusters (grid = clusters * splits)
+  int splits;          // CTAs per cluster = split-K factor
+  int total_blocks;    // ceil(N / 8)
+  int chunks;          // ceil(K / 1024)
+  int ring_scales;     // 1: the chunk's scales travel through the ring with the weights
+};
+
+// One TMA op: the 2-D box at element coordinates (c0, c1) of `map` -> dense rows at dst; completes on `bar`.
+__device__ __forceinline__ void tma_box_2d(void* dst_smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst_smem)),
+      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+
+template <bool ROWS16>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+w4a16_stream_kernel(W4Args a, StreamPlan plan, const __grid_constant__ CUtensorMap wmap,
+                    const __grid_constant__ CUtensorMap smap) {
+  constexpr int kRows = ROWS16 ? 16 : 8;
+  constexpr int kXUnits = kChunkK / 8;  // 16-byte units per staged x row
+  constexpr int kPassBlocks = kStreamWarps * kMaxNB;
+  constexpr int kDepth = StreamDepth<ROWS16>::value;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, j = lane & 3;
+  unsigned char* ring = smem_raw + warp * kDepth * kSlotBytes;                          // this warp's slots
+  U4* xs = reinterpret_cast<U4*>(smem_raw + kStreamWarps * kDepth * kSlotBytes);       // [2][kRows][kXUnits]
+  float* part = reinterpret_cast<float*>(smem_raw + kStreamWarps * kDepth * kSlotBytes + 2 * kRows * kChunkK * 2);
+  uint64_t* full = reinterpret_cast<uint64_t*>(part + 16 * kStreamWarps * kMaxNB * 8) + warp * kDepth;  // this warp's barriers
+  if (lane == 0) {
+    for (int i = 0; i < kDepth; ++i) mbar_init(full + i, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+
+  const int rank = plan.splits > 1 ? static_cast<int>(cg::this_cluster().block_rank()) : 0;
+  const int cluster_id = blockIdx.x / plan.splits;
+  // even deal of column blocks to clusters
+  const int blk_begin = static_cast<int>(static_cast<int64_t>(cluster_id) * plan.total_blocks / plan.clusters);
+  const int blk_end = static_cast<int>(static_cast<int64_t>(cluster_id + 1) * plan.total_blocks / plan.clusters);
+  const int nblk = blk_end - blk_begin;
+  const int my_chunks = plan.chunks > rank ? (plan.chunks - rank + plan.splits - 1) / plan.splits : 0;
+  const int row_bytes = a.k / 2;
+  const int scale_shift = 31 - __clz(a.group);  // group is a power of two
+
+  // ---- prefetch side: walks the same (pass, chunk, block) sequence as the compute loop, ahead of it
+  int pf_p0 = 0, pf_ci = 0, pf_b = warp, pf_q = 0;
+  bool pf_valid = my_chunks > 0 && nblk > 0;
+  auto pf_normalize = [&]() {
+    while (pf_valid && pf_b >= min(kPassBlocks, nblk - pf_p0)) {
+      pf_b = warp;
+      if (++pf_ci >= my_chunks) {
+        pf_ci = 0;
+        pf_p0 += kPassBlocks;
+        if (pf_p0 >= nblk) pf_valid = false;
+      }
+    }
+  };
+  const unsigned tile_bytes = 8 * kRowStride + (plan.ring_scales ? 8u * ((kChunkK >> scale_shift) * 2) : 0u);
+  auto pf_issue = [&]() {  // TMA ops for the next tile of this warp (if any) into slot pf_q % kDepth
+    pf_normalize();
+    if (pf_valid) {
+      if (lane == 0) {
+        const int kc = rank + pf_ci * plan.splits;
+        const int col0 = (blk_begin + pf_p0 + pf_b) * 8;
+        unsigned char* dst = ring + (pf_q % kDepth) * kSlotBytes;
+        uint64_t* bar = full + pf_q % kDepth;
+        mbar_expect_tx(bar, tile_bytes);  // out-of-range parts of a box are zero-filled and still counted
+        tma_box_2d(dst, &wmap, kc * (kChunkK / 8), col0, bar);
+        if (plan.ring_scales) tma_box_2d(dst + 8 * kRowStride, &smap, kc * (kChunkK >> scale_shift), col0, bar);
+      }
+      pf_b += kStreamWarps;
+      ++pf_q;
+    }
+  };
+#pragma unroll
+  for (int d = 0; d < kDepth - 1; ++d) pf_issue();
+
+  int q = 0;  // tiles this warp has consumed
+  for (int p0 = 0; p0 < nblk; p0 += kPassBlocks) {
+    const int nb_pass = min(kPassBlocks, nblk - p0);
+    const int cols = nb_pass * 8;  // width of part[16][cols] for this pass
+
+    // x staging.  A thread owns kStage 16-byte units of every chunk.  The first chunk of a pass is
+    // staged at once; the next chunk is staged two units at a time around the tiles of the current
+    // one (loads issued before a tile, permuted and stored after it) so that only two units are
+    // ever live in registers during the unpack/mma loop.
+    constexpr int kStage = kRows * kXUnits / kStreamThreads;  // units per thread per chunk
+    auto x_load = [&](int kc, int i) -> U4 {
+      const int idx = threadIdx.x + i * kStreamThreads;
+      const int r = idx / kXUnits, u = idx - r * kXUnits;
+      const int k0 = kc * kChunkK + u * 8;
+      U4 v = U4{0u, 0u, 0u, 0u};
+      if (r < a.m && k0 < a.k) v = ld_cached16(a.x + static_cast<size_t>(r) * a.k + k0);
+      return v;
+    };
+    auto x_store = [&](int buf, int i, const U4& t) {
+      const int idx = threadIdx.x + i * kStreamThreads;
+      const int r = idx / kXUnits, u = idx - r * kXUnits;
+      U4 v;
+      v.x = __byte_perm(t.x, t.z, 0x5410);
+      v.y = __byte_perm(t.x, t.z, 0x7632);
+      v.z = __byte_perm(t.y, t.w, 0x5410);
+      v.w = __byte_perm(t.y, t.w, 0x7632);
+      xs[(buf * kRows + r) * kXUnits + xunit(u, r)] = v;
+    };
+    if (my_chunks > 0) {
+      U4 first[kStage];
+#pragma unroll
+      for (int i = 0; i < kStage; ++i) first[i] = x_load(rank, i);
+#pragma unroll
+      for (int i = 0; i < kStage; ++i) x_store(0, i, first[i]);
+    }
+    __syncthreads();
+
+    for (int ci = 0; ci < my_chunks; ++ci) {
+      const int kc = rank + ci * plan.splits;
+      const int steps = min(kChunkK, a.k - kc * kChunkK) / 128;
+      const bool more = ci + 1 < my_chunks;
+      const bool last = !more;
+      int staged = more ? 0 : kStage;  // units of the next chunk this thread has staged so far
+      const U4* xb = xs + (ci & 1) * kRows * kXUnits;
+      for (int b = warp; b < nb_pass; b += kStreamWarps, ++q) {
+        const bool stage_now = staged < kStage;
+        U4 nx0 = U4{0u, 0u, 0u, 0u}, nx1 = U4{0u, 0u, 0u, 0u};
+        if (stage_now) {
+          nx0 = x_load(kc + plan.splits, staged);
+          nx1 = x_load(kc + plan.splits, staged + 1);
+        }
+        const int col = (blk_begin + p0 + b) * 8 + g;
+        // Slow path only (scales not in the ring): this lane's scale for every step, fetched before the wait
+        __half sc[8];
+        if (!plan.ring_scales) {
+#pragma unroll
+          for (int st = 0; st < 8; ++st) {
+            sc[st] = __float2half(0.0f);
+            if (st < steps && col < a.n)
+              sc[st] = __ldg(a.scales + static_cast<size_t>(col) * a.groups + ((kc * kChunkK + st * 128 + j * 32) >> scale_shift));
+          }
+        }
+        pf_issue();  // refill the slot freed by the previous tile
+        const bool landed = mbar_wait(full + q % kDepth, (q / kDepth) & 1);
+        const unsigned char* slot = ring + (q % kDepth) * kSlotBytes;
+        const unsigned char* tile = slot + g * kRowStride + j * 16;
+        const __half* tile_scales =
+            reinterpret_cast<const __half*>(slot + 8 * kRowStride + g * ((kChunkK >> scale_shift) * 2));
+        if (!landed) atomicOr(&g_w4_fault, 1u);
+        float part4[8][4];  // eight independent accumulator chains hide the mma latency
+#pragma unroll
+        for (int w = 0; w < 8; ++w)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) part4[w][e] = 0.0f;
+#pragma unroll
+        for (int st = 0; st < 8; ++st) {
+          if (st >= steps || !landed) break;
+          U4 wv = U4{0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};
+          __half s1 = __float2half(0.0f);
+          if (col < a.n) {
+            wv = *reinterpret_cast<const U4*>(tile + st * 64);
+            s1 = plan.ring_scales ? tile_scales[(st * 128 + j * 32) >> scale_shift] : sc[st];
+          }
+          const __half2 s2 = __half2half2(s1);
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const int unit = st * 16 + j * 4 + w;
+            const U4 xa = xb[g * kXUnits + xunit(unit, g)];
+            U4 xc = U4{0u, 0u, 0u, 0u};
+            if constexpr (ROWS16) xc = xb[(g + 8) * kXUnits + xunit(unit, g + 8)];
+            const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
+            __half2 h[4];
+            dequant8(word, s2, h);
+            mma16816(part4[2 * w], xa.x, xc.x, xa.y, xc.y, *reinterpret_cast<uint32_t*>(&h[0]),
+                     *reinterpret_cast<uint32_t*>(&h[1]));
+            mma16816(part4[2 * w + 1], xa.z, xc.z, xa.w, xc.w, *reinterpret_cast<uint32_t*>(&h[2]),
+                     *reinterpret_cast<uint32_t*>(&h[3]));
+          }
+        }
+        __syncwarp();  // every lane is done reading the slot before the next pf_issue overwrites it
+
+        // C[row g][2j], C[g][2j+1], C[g+8][2j], C[g+8][2j+1] of this block for this chunk
+        float c4[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          c4[e] = ((part4[0][e] + part4[1][e]) + (part4[2][e] + part4[3][e])) + ((part4[4][e] + part4[5][e]) + (part4[6][e] + part4[7][e]));
+        float* mine = part + g * cols + b * 8 + 2 * j;  // rows g and g+8 of part[16][cols]; only this lane touches them
+        if (ci > 0) {
+          c4[0] += mine[0], c4[1] += mine[1];
+          c4[2] += mine[8 * cols], c4[3] += mine[8 * cols + 1];
+        }
+        if (last && plan.splits == 1) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int row = g + (e >> 1) * 8, oc = (blk_begin + p0 + b) * 8 + 2 * j + (e & 1);
+            if (row < a.m && oc < a.n) {
+              const float bv = a.bias ? __half2float(a.bias[oc]) : 0.0f;
+              a.y[static_cast<size_t>(row) * a.n + oc] = __float2half_rn(c4[e] + bv);
+            }
+          }
+        } else {
+          mine[0] = c4[0], mine[1] = c4[1];
+          mine[8 * cols] = c4[2], mine[8 * cols + 1] = c4[3];
+        }
+        if (stage_now) {
+          x_store((ci + 1) & 1, staged, nx0);
+          x_store((ci + 1) & 1, staged + 1, nx1);
+          staged += 2;
+        }
+      }
+      for (; staged < kStage; ++staged) x_store((ci + 1) & 1, staged, x_load(kc + plan.splits, staged));
+      __syncthreads();
+    }
+  }
+  if (plan.splits > 1) {
+    // The host guarantees a single pass when K is split, so part[16][nblk * 8] is complete here.
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int cols = nblk * 8;
+    const int total = 16 * cols;
+    const int share = (total + plan.splits - 1) / plan.splits;
+    for (int i = threadIdx.x; i < share; i += kStreamThreads) {
+      const int o = rank * share + i;
+      if (o < total) {
+        const int row = o / cols, c = o - row * cols;
+        const int col = blk_begin * 8 + c;
+        float v = 0.0f;
+        for (int sidx = 0; sidx < plan.splits; ++sidx) v += *cluster.map_shared_rank(part + o, sidx);
+        if (row < a.m && col < a.n) {
+          const float bv = a.bias ? __half2float(a.bias[col]) : 0.0f;
+          a.y[static_cast<size_t>(row) * a.n + col] = __float2half_rn(v + bv);
+        }
+      }
+    }
+    cluster.sync();
+  }
+}
+
+// cuTensorMapEncodeTiled comes from the driver; fetch it through the runtime so that the library
+// needs no link-time dependency on libcuda.
+bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t* dims,
+                     const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+  using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Encode encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    encode = reinterpret_cast<Encode>(fn);
+  }
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return encode(map, type, 2, const_cast<void*>(base), dims, strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool ROWS16>
+int launch_stream(const W4Args& a, cudaStream_t stream) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      sm_count = 148;
+  }
+  StreamPlan plan;
+  plan.total_blocks = (a.n + 7) / 8;
+  plan.chunks = (a.k + kChunkK - 1) / kChunkK;
+  plan.ring_scales = (a.group <= 128 && a.k % kChunkK == 0 && aligned16(a.scales)) ? 1 : 0;
+  constexpr int kDepth = StreamDepth<ROWS16>::value;
+  const size_t smem = static_cast<size_t>(kStreamWarps) * kDepth * kSlotBytes + 2 * (ROWS16 ? 16 : 8) * kChunkK * 2 +
+                      16 * kStreamWarps * kMaxNB * 8 * sizeof(float) + kStreamWarps * kDepth * sizeof(uint64_t);
+  CUtensorMap wmap, smap;
+  {
+    // packed weights as a [N][K/8] matrix of 32-bit words; box = 8 rows x 128 words (1024 k)
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k / 8), static_cast<cuuint64_t>(a.n)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k / 2)};
+    const cuuint32_t box[2] = {kChunkK / 8, 8};
+    if (!encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.packed, dims, strides, box)) return XDK_ERR_LAUNCH;
+    smap = wmap;
+    if (plan.ring_scales) {
+      const cuuint64_t sdims[2] = {static_cast<cuuint64_t>(a.groups), static_cast<cuuint64_t>(a.n)};
+      const cuuint64_t sstrides[1] = {static_cast<cuuint64_t>(a.groups) * 2};
+      const cuuint32_t sbox[2] = {static_cast<cuuint32_t>(kChunkK / a.group), 8};
+      if (!encode_tiled_2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, sdims, sstrides, sbox)) return XDK_ERR_LAUNCH;
+    }
+  }
+  auto kernel = w4a16_stream_kernel<ROWS16>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (err != cudaSuccess) return note_launch(err);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kStreamThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+
+  // How many clusters of S CTAs fit on the device at once (1 CTA per SM; a cluster must sit inside
+  // one GPC, so this is not simply SMs / S).  Asked once per S, then cached.
+  static int resident[3] = {0, 0, 0};  // S = 1, 2, 4
+  auto resident_clusters = [&](int s_log2) {
+    if (resident[s_log2] == 0) {
+      const int sz = 1 << s_log2;
+      int n = 0;
+      if (sz == 1) {
+        n = sm_count;
+      } else {
+        cfg.gridDim = dim3(sm_count / sz * sz);
+        attr[0].val.clusterDim.x = sz;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+          (void)cudaGetLastError();
+          n = 0;
+        }
+      }
+      resident[s_log2] = n > 0 ? n : -1;
+    }
+    return resident[s_log2] > 0 ? resident[s_log2] : 0;
+  };
+  // Split K over a cluster so that each CTA stages only 1/S of x, as long as (a) the whole grid stays
+  // resident in one wave, (b) it does not idle more than ~6 % of the SMs, and (c) the cluster can
+  // finish its blocks in one pass (partial sums are parked in shared memory).
+  int best_log2 = 0;
+  for (int s_log2 = 2; s_log2 >= 1; --s_log2) {
+    const int sz = 1 << s_log2;
+    if (sz > plan.chunks) continue;
+    const int fit = resident_clusters(s_log2);
+    if (fit * sz * 100 < sm_count * 94) continue;
+    const int clusters = min(fit, plan.total_blocks);
+    if ((plan.total_blocks + clusters - 1) / clusters > kStreamWarps * kMaxNB) continue;
+    best_log2 = s_log2;
+    break;
+  }
+  plan.splits = 1 << best_log2;
+  plan.clusters = min(resident_clusters(best_log2), plan.total_blocks);
+  if (plan.clusters <= 0) plan.clusters = min(sm_count, plan.total_blocks), plan.splits = 1;
+  cfg.gridDim = dim3(plan.clusters * plan.splits);
+  attr[0].val.clusterDim.x = plan.splits;
+  cfg.numAttrs = plan.splits > 1 ? 1 : 0;
+  return note_launch(cudaLaunchKernelEx(&cfg, kernel, a, plan, wmap, smap));
+}
+
+
 // Any K (odd included), any alignment: warp per column, lane per byte (two codes), rows one at a
 // time.  Slow; it exists so that every shape the format allows has a GPU path.
 __global__ void __launch_bounds__(kThreads)
@@ -215,6 +620,9 @@ extern "C" int xdk_w4a16(const void* x, const uint8_t* packed, const void* scale
   a.col_groups = a.groups_per_cta = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool fast = k % 32 == 0 && aligned16(packed) && aligned16(x) && m * k * 2 <= 200 * 1024;
+  if (fast && k % 128 == 0 && m >= 3) {
+    return m > 8 ? launch_stream<true>(a, s) : launch_stream<false>(a, s);
+  }
   if (fast) {
     if (m == 1) return launch_simt<1, 2>(a, s);
     if (m == 2) return launch_simt<2, 2>(a, s);

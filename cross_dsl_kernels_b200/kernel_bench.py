@@ -1,0 +1,144 @@
+"""Per-kernel CUDA-graph medians for the decode ops at their headline shapes.
+
+Each row times one op at one shape: a CUDA graph of back-to-back calls that
+rotate over enough distinct buffer sets to defeat the L2 (see timing.py),
+replayed and event-timed; ``gbps`` is the op's algorithmic bytes over the
+per-call median.  Used by bench.py and usable on its own:
+
+    python -m cross_dsl_kernels_b200.kernel_bench [rmsnorm|gemv|rope|w4a16] ...
+"""
+
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from . import workloads as wl
+from .ops import decode_linear, fused_residual_rmsnorm, rope_gqa_paged_kv_append
+from .timing import graph_median_us, rotation_for
+from .w4a16 import w4a16_linear
+
+NOMINAL_HBM_GBPS = 8000.0
+
+
+def _row(name: str, nbytes: int, timing: dict, sets: int, peak_gbps: float | None, **extra) -> dict:
+    us = timing["median_us"]
+    gbps = nbytes / us * 1e-3
+    row = {"kernel": name, "us": round(us, 3), "bytes": nbytes, "gbps": round(gbps, 1),
+           "frac_of_8tbs": round(gbps / NOMINAL_HBM_GBPS, 4), "buffer_sets": sets,
+           "p10_us": round(timing["p10_us"], 3), "p90_us": round(timing["p90_us"], 3)}
+    if peak_gbps:
+        row["frac_of_measured"] = round(gbps / peak_gbps, 4)
+    row.update(extra)
+    return row
+
+
+def _calls_per_graph(sets: int) -> int:
+    return sets * max(1, -(-20 // sets))  # at least 20 calls, whole rotations
+
+
+def bench_rmsnorm(rows: int, hidden: int, dtype, peak=None, replays=20) -> dict:
+    nbytes = wl.rmsnorm_bytes(rows, hidden, dtype)
+    sets = rotation_for(nbytes)
+    x, r, w = (t.cuda() for t in wl.rmsnorm_inputs(rows, hidden, dtype))
+    data = [(x.roll(s, 0), r.roll(s, 0), w) if s else (x, r, w) for s in range(sets)]
+    n = _calls_per_graph(sets)
+    calls = [(lambda d=data[i % sets]: fused_residual_rmsnorm(d[0], d[1], d[2], 1e-6)) for i in range(n)]
+    t = graph_median_us(calls, replays)
+    name = f"rmsnorm_{str(dtype).split('.')[-1]}_{rows}x{hidden}"
+    return _row(name, nbytes, t, sets, peak)
+
+
+def bench_gemv(m: int, k: int, n: int, layout: str, split_k: int = 0, bias=True, peak=None, replays=20) -> dict:
+    nbytes = wl.projection_bytes(m, k, n, bias)
+    sets = rotation_for(nbytes, cap=8)
+    x, w, b = wl.projection_inputs(m, k, n, layout, bias)
+    xd, bd = x.cuda(), (b.cuda() if bias else None)
+    ws = [w.cuda()] + [torch.empty_like(w, device="cuda").normal_(0, k ** -0.5) for _ in range(sets - 1)]
+    ncalls = _calls_per_graph(sets)
+    calls = [(lambda wt=ws[i % sets]: decode_linear(xd, wt, bd, weight_layout=layout, split_k=split_k)) for i in range(ncalls)]
+    t = graph_median_us(calls, replays)
+    return _row(f"gemv_f32_{layout}_m{m}_k{k}_n{n}_s{split_k}", nbytes, t, sets, peak, split_k=split_k)
+
+
+def bench_rope(dtype, layout: str, rope_dim: int, peak=None, replays=20, **shape) -> dict:
+    case = wl.rope_inputs(rope_dim=rope_dim, layout=layout, dtype=dtype, **shape)
+    tokens, hq, dim = case["q"].shape
+    hkv = case["k"].shape[1]
+    nbytes = wl.rope_bytes(tokens, hq, hkv, dim, rope_dim, dtype)
+    sets = 8
+    dev = {key: (val.cuda() if torch.is_tensor(val) else val) for key, val in case.items()}
+    kc = torch.full(case["cache_shape"], -999.0, dtype=dtype, device="cuda")
+    vc = torch.full_like(kc, -999.0)
+    qs = [dev["q"].roll(s, 0) for s in range(sets)]
+    calls = [(lambda q=qs[i % sets]: rope_gqa_paged_kv_append(
+        q, dev["k"], dev["v"], dev["cos"], dev["sin"], dev["positions"], dev["page_table"], dev["sequence_ids"], kc, vc,
+        page_size=case["page_size"], rope_dim=rope_dim, interleaved=False, kv_layout=layout)) for i in range(24)]
+    t = graph_median_us(calls, replays)
+    name = f"rope_kv_{str(dtype).split('.')[-1]}_{layout}_rd{rope_dim}_t{tokens}"
+    return _row(name, nbytes, t, sets, peak)
+
+
+def bench_w4a16(m: int, k: int, n: int, group: int = 128, peak=None, replays=20) -> dict:
+    nbytes = wl.w4a16_bytes(m, k, n, group)
+    sets = rotation_for(nbytes, cap=48)
+    x, packed, scales, _ = wl.w4a16_inputs(m, k, n, group)
+    xd, sd = x.cuda(), scales.cuda()
+    ps = [packed.cuda()] + [torch.randint(0, 256, packed.shape, dtype=torch.uint8, device="cuda") for _ in range(sets - 1)]
+    ss = [sd] + [sd.clone() for _ in range(sets - 1)]
+    outs = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in range(sets)]
+    ncalls = _calls_per_graph(sets)
+    calls = [(lambda i=i: w4a16_linear(xd, ps[i % sets], ss[i % sets], None, group_size=group, out=outs[i % sets])) for i in range(ncalls)]
+    t = graph_median_us(calls, replays)
+    return _row(f"w4a16_m{m}_k{k}_n{n}_g{group}", nbytes, t, sets, peak)
+
+
+def table(which=("rmsnorm", "gemv", "rope", "w4a16"), peak=None, split_sweep=True) -> list[dict]:
+    rows = []
+    if "rmsnorm" in which:
+        for dtype in (torch.float32, torch.bfloat16):
+            for r in (256, 4096):
+                rows.append(bench_rmsnorm(r, 4096, dtype, peak))
+    if "gemv" in which:
+        for layout in ("KN", "NK"):
+            for n in (4096, 14336):
+                for m in (1, 4, 16):
+                    for s in ((0, 1, 2, 4, 8) if split_sweep else (0,)):
+                        rows.append(bench_gemv(m, 4096, n, layout, s, True, peak))
+    if "rope" in which:
+        for dtype in (torch.float32, torch.bfloat16):
+            for layout in ("NHD", "HND"):
+                for rd in (64, 128):
+                    rows.append(bench_rope(dtype, layout, rd, peak))
+    if "w4a16" in which:
+        for n in (4096, 14336):
+            for m in (1, 16):
+                rows.append(bench_w4a16(m, 4096, n, 128, peak))
+    return rows
+
+
+def one(argv: list[str]) -> dict:
+    """``--one rmsnorm ROWS HIDDEN f32|bf16|f16`` | ``--one gemv M K N KN|NK SPLIT`` |
+    ``--one rope f32|bf16 NHD|HND ROPE_DIM`` | ``--one w4a16 M K N GROUP``; few replays (for profilers)."""
+    dtypes = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
+    op, rest = argv[0], argv[1:]
+    if op == "rmsnorm":
+        return bench_rmsnorm(int(rest[0]), int(rest[1]), dtypes[rest[2]], replays=3)
+    if op == "gemv":
+        return bench_gemv(int(rest[0]), int(rest[1]), int(rest[2]), rest[3], int(rest[4]), replays=3)
+    if op == "rope":
+        return bench_rope(dtypes[rest[0]], rest[1], int(rest[2]), replays=3)
+    if op == "w4a16":
+        return bench_w4a16(int(rest[0]), int(rest[1]), int(rest[2]), int(rest[3]), replays=3)
+    raise SystemExit(one.__doc__)
+
+
+if __name__ == "__main__":
+    if len(sys.argv) > 2 and sys.argv[1] == "--one":
+        print(json.dumps(one(sys.argv[2:])))
+        raise SystemExit(0)
+    chosen = tuple(sys.argv[1:]) or ("rmsnorm", "gemv", "rope", "w4a16")
+    for row in table(chosen):
+        print(json.dumps(row))
