@@ -255,6 +255,10 @@ def main() -> None:
            "d2h_bytes_per_step": sum(4 * m * n // world for m, n, _ in SWEEP),
            "ms_per_step": round(float(e2e_s.item()) * 1e3, 4)}
 
+    chain_row = None
+    if not args.no_table:
+        chain_row = kernel_bench.bench_chain(rank=rank, world=world, peak=peaks["hbm_gbs"])
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -273,6 +277,8 @@ def main() -> None:
                      "kernel": "gemv_kn_kernel / gemv_nk_kernel (12 launches per step)",
                      "note": "achieved = sweep algorithmic bytes / step device time, per GPU"},
     }
+    if chain_row is not None:
+        line["chain"] = chain_row
     if world == 1:
         line["cpu_baseline"] = {k: v for k, v in time_cpu_sweep(20, 2, budget_s=20.0).items()
                                 if k in ("value", "unit", "cores", "kind", "sample")}

@@ -28,6 +28,7 @@ SIGNATURES = {
     "xdk_gemv_f32": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p]),
     "xdk_rope_kv_append": (_int, [_p] * 11 + [_i64] * 11 + [_int, _int, _int, _p]),
     "xdk_w4a16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _p]),
+    "xdk_unshard_columns": (_int, [_p, _p, _i64, _i64, _i64, _int, _p]),
 }
 
 

@@ -95,6 +95,32 @@ def bench_w4a16(m: int, k: int, n: int, group: int = 128, peak=None, replays=20)
     return _row(f"w4a16_m{m}_k{k}_n{n}_g{group}", nbytes, t, sets, peak)
 
 
+def bench_chain(rank: int = 0, world: int = 1, layers: int = 4, peak=None, replays=20, group=None) -> dict:
+    """Decode-layer chain: ``layers`` layers with distinct weights (more than L2 in total) in one
+    CUDA graph; reports the per-layer median.  With world > 1 every rank must call this."""
+    from .chain import ChainConfig, DecodeLayerChain
+    from .timing import capture, replay_times_ms
+    import statistics
+
+    cfg = ChainConfig()
+    chain = DecodeLayerChain(cfg, layers=layers, rank=rank, world=world, group=group)
+    graph = capture([chain.run_layers])
+    times = replay_times_ms(graph, replays, 3)
+    us = statistics.median(times) * 1e3 / layers
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([us], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        us = float(t.item())
+    nbytes = cfg.algorithmic_bytes()
+    row = {"kernel": f"decode_layer_chain_fp16_t{cfg.tokens}_h{cfg.hidden}_ctx{cfg.context}", "us": round(us, 3),
+           "bytes": nbytes, "gbps": round(nbytes / us * 1e-3, 1), "frac_of_8tbs": round(nbytes / us * 1e-3 / (NOMINAL_HBM_GBPS * world), 4),
+           "n_gpus": world, "layers_in_graph": layers, "launches_per_layer": chain.launches_per_layer}
+    if peak:
+        row["frac_of_measured"] = round(nbytes / us * 1e-3 / (peak * world), 4)
+    return row
+
+
 def table(which=("rmsnorm", "gemv", "rope", "w4a16"), peak=None, split_sweep=True) -> list[dict]:
     rows = []
     if "rmsnorm" in which:
@@ -116,6 +142,8 @@ def table(which=("rmsnorm", "gemv", "rope", "w4a16"), peak=None, split_sweep=Tru
         for n in (4096, 14336):
             for m in (1, 16):
                 rows.append(bench_w4a16(m, 4096, n, 128, peak))
+    if "chain" in which:
+        rows.append(bench_chain(peak=peak))
     return rows
 
 
@@ -139,6 +167,6 @@ if __name__ == "__main__":
     if len(sys.argv) > 2 and sys.argv[1] == "--one":
         print(json.dumps(one(sys.argv[2:])))
         raise SystemExit(0)
-    chosen = tuple(sys.argv[1:]) or ("rmsnorm", "gemv", "rope", "w4a16")
+    chosen = tuple(sys.argv[1:]) or ("rmsnorm", "gemv", "rope", "w4a16", "chain")
     for row in table(chosen):
         print(json.dumps(row))

@@ -126,6 +126,15 @@ XDK_API int xdk_rope_kv_append(const void* q, const void* k, const void* v, cons
 XDK_API int xdk_w4a16(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
               int64_t m, int64_t k, int64_t n, int group_size, void* stream);
 
+/*
+ * Multi-GPU helper with no upstream counterpart (upstream is single-GPU): after an all-gather of
+ * column shards, `gathered` holds [world, rows, cols_per_rank] (rank-major); this writes the
+ * row-major matrix out[rows, world * cols_per_rank] in which rank r owns columns
+ * [r * cols_per_rank, (r + 1) * cols_per_rank).  elem_bytes in {1,2,4,8}.  out must not alias gathered.
+ */
+XDK_API int xdk_unshard_columns(const void* gathered, void* out, int64_t world, int64_t rows,
+                                int64_t cols_per_rank, int elem_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,58 @@
+"""Host logic of the multi-GPU path on CPU: two gloo ranks each compute their
+column shard of the chain's two projections with the CPU oracle, all-gather the
+shards rank-major and un-shard them; the result must equal the unsharded
+projection (QKV up to the documented column order, up+gate exactly in place)."""
+
+from __future__ import annotations
+
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, ok):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cross_dsl_kernels_b200.chain import (ChainConfig, _quantised, qkv_shard_rows, unshard_reference,
+                                                  upgate_shard_rows)
+        from oracle import int4
+        cfg = ChainConfig(tokens=4, hidden=256, q_heads=4, kv_heads=2, head_dim=32, mlp=192, context=64)
+        gen = torch.Generator().manual_seed(0)  # same weights on every rank
+        qkv_p, qkv_s = _quantised(cfg.qkv_cols, cfg.hidden, cfg.group, gen)
+        up_p, up_s = _quantised(2 * cfg.mlp, cfg.hidden, cfg.group, gen)
+        x = torch.randn(cfg.tokens, cfg.hidden, generator=gen).half()
+        for packed, scales, rows_fn in ((qkv_p, qkv_s, qkv_shard_rows), (up_p, up_s, upgate_shard_rows)):
+            rows = rows_fn(cfg, rank, world)
+            shard = int4.w4a16_projection(x, packed[rows].contiguous(), scales[rows].contiguous(), group_size=cfg.group)
+            parts = [torch.empty_like(shard) for _ in range(world)]
+            dist.all_gather(parts, shard)  # rank-major, like all_gather_into_tensor on the GPU path
+            gathered = torch.stack(parts)
+            full = int4.w4a16_projection(x, packed, scales, group_size=cfg.group)
+            order = torch.cat([rows_fn(cfg, r, world) for r in range(world)])
+            assert sorted(order.tolist()) == list(range(packed.shape[0])), "shards must partition the columns"
+            assert torch.equal(unshard_reference(gathered), full[:, order])
+        # KV heads: rank r appends exactly heads [r*Hkv/g, (r+1)*Hkv/g) -- the K/V part of its QKV rows
+        d, hkv = cfg.head_dim, cfg.kv_heads // world
+        rows = qkv_shard_rows(cfg, rank, world)
+        k_rows = rows[cfg.q_heads // world * d: cfg.q_heads // world * d + hkv * d]
+        assert k_rows[0].item() == cfg.q_heads * d + rank * hkv * d
+        ok[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_sharding_with_two_gloo_ranks():
+    world = 2
+    ok = mp.get_context("spawn").Array("i", [0] * world)
+    mp.spawn(_worker, args=(world, _free_port(), ok), nprocs=world, join=True)
+    assert list(ok) == [1] * world
