@@ -260,9 +260,7 @@ def main() -> None:
         chain_row = kernel_bench.bench_chain(rank=rank, world=world, peak=peaks["hbm_gbs"])
 
     if rank != 0:
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
+        finish(world)
         return
 
     clocks = sampler.summary()
@@ -286,9 +284,21 @@ def main() -> None:
             rows = kernel_bench.table(peak=peaks["hbm_gbs"], split_sweep=True)
             line["kernels"] = rows
     print(json.dumps(line), flush=True)
+    finish(world)
+
+
+def finish(world: int) -> None:
+    """Multi-rank exit: meet once more, then leave without tearing NCCL down (communicators that
+    CUDA graphs still reference do not always unwind cleanly; the process is ending anyway)."""
     if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
