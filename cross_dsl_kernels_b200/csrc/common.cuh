@@ -1,6 +1,7 @@
 // Shared device/host helpers for the sm_100a decode kernels.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -16,6 +17,13 @@ namespace xdk {
 int note_launch(cudaError_t err);
 // XDK_OK when the device current to this thread is compute capability 10.x (cached per device).
 int require_sm100();
+
+// Encodes a 2-D tiled TMA tensor map (dims/box innermost first, strides in bytes for dim 1).
+// cuTensorMapEncodeTiled is fetched from the driver through the runtime, so the library has no
+// link-time dependency on libcuda.  swizzle128: 128-byte swizzle (inner box must be 128 bytes).
+bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t* dims,
+                     const cuuint64_t* strides_bytes, const cuuint32_t* box, bool swizzle128);
+int sm_count();  // SMs of the current device (cached per device)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -148,7 +156,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, uint64
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
         : "r"(addr), "r"(parity)

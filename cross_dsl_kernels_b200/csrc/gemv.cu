@@ -334,6 +334,236 @@ gemv_nk_kernel(GemvArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// M > 4: the op is bound by FP32 FMA issue (MT FMAs per weight element), so every SM has to get the
+// same amount of work and its warps must never wait on global memory.
+//
+// Persistent kernel, one CTA per SM.  The weight matrix is cut into tiles of 32 k x 128 columns;
+// tiles are numbered strip-major (all K tiles of column strip 0, then strip 1, ...) and CTA c takes
+// the contiguous range [c*T/G, (c+1)*T/G): every CTA gets the same number of tiles (+-1) whatever
+// N is.  A producer lane streams tiles with TMA tensor-map box copies (16 KB of W plus the matching
+// 32-k slice of x, zero-filled outside M, N and K) into an 8-stage shared-memory ring; sixteen
+// consumer warps each own one k-quad and one 64-column half of every tile and run pure shared-load +
+// FMA code on an MT x 2 register tile (four warps per scheduler keep the FMA pipe busy).  KN tiles are read row-wise; NK tiles arrive 128-byte swizzled so that
+// lanes reading different columns at the same k hit different banks.
+// A strip that falls entirely inside one CTA's range is finished there (bias, store).  A strip cut
+// by a range boundary leaves one partial [MT][128] per contributing CTA in the caller's scratch
+// buffer and gemv_stream_finish_kernel adds them in CTA order: deterministic, no atomics.
+constexpr int kTileK = 32, kTileN = 128;
+constexpr int kTileStages = 8;
+constexpr int kTileCtasPerSm = 1;
+constexpr int kTileConsumers = 16;  // 8 k-quads x 2 column halves of a tile
+constexpr int kTileThreads = (kTileConsumers + 1) * 32;
+constexpr int kTileWBytes = kTileK * kTileN * 4;  // 16 KB
+
+__device__ unsigned int g_gemv_fault;  // set when a bounded wait gives up
+
+struct TileArgs {
+  const float* bias;
+  float* y;
+  float* scratch;  // [ctas][2][MT][128]
+  int m, k, n;
+  int strips, k_tiles;  // column strips, K tiles per strip
+  int ctas;
+};
+
+__device__ __forceinline__ void tma_tile_2d(void* dst_smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst_smem)),
+      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kTileConsumers * 32) : "memory"); }
+
+__host__ __device__ __forceinline__ int64_t tile_begin(int cta, int64_t total, int ctas) {
+  return static_cast<int64_t>(cta) * total / ctas;
+}
+
+// Two independent FP32 FMAs in one instruction (sm_100): d.lo += a.lo*b.lo, d.hi += a.hi*b.hi, each
+// rounded exactly like a scalar fma.rn.f32.
+__device__ __forceinline__ void ffma2(float2& acc, float2 a, float2 b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;"
+      : "+l"(reinterpret_cast<uint64_t&>(acc))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+}
+
+template <int MT, bool NK>
+__global__ void __launch_bounds__(kTileThreads, kTileCtasPerSm)
+gemv_stream_kernel(TileArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
+  constexpr int kStageBytes = kTileWBytes + MT * kTileK * 4;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* ring = smem_raw;
+  constexpr int RH = MT / 2;  // the cross-warp fold runs in two rounds of MT/2 rows to halve its buffer
+  float* red = reinterpret_cast<float*>(smem_raw + kTileStages * kStageBytes);  // [8][MT/2][128]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + 8 * RH * kTileN);
+  uint64_t* empty = full + kTileStages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t total = static_cast<int64_t>(a.strips) * a.k_tiles;
+  const int64_t t_begin = tile_begin(blockIdx.x, total, a.ctas), t_end = tile_begin(blockIdx.x + 1, total, a.ctas);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kTileStages; ++i) {
+      mbar_init(full + i, 1);
+      mbar_init(empty + i, kTileConsumers);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kTileConsumers) {
+    // ---------------------------------------------------------------- producer (one lane)
+    if (lane == 0) {
+      int strip = static_cast<int>(t_begin / a.k_tiles);
+      int kt = static_cast<int>(t_begin - static_cast<int64_t>(strip) * a.k_tiles);
+      const int n_tiles = static_cast<int>(t_end - t_begin);
+      for (int q = 0; q < n_tiles; ++q) {
+        const int s = q % kTileStages;
+        if (q >= kTileStages && !mbar_wait(empty + s, ((q / kTileStages) - 1) & 1)) {
+          atomicOr(&g_gemv_fault, 1u);
+          break;
+        }
+        unsigned char* dst = ring + s * kStageBytes;
+        mbar_expect_tx(full + s, kStageBytes);
+        if (NK) tma_tile_2d(dst, &wmap, kt * kTileK, strip * kTileN, full + s);
+        else tma_tile_2d(dst, &wmap, strip * kTileN, kt * kTileK, full + s);
+        tma_tile_2d(dst + kTileWBytes, &xmap, kt * kTileK, 0, full + s);
+        if (++kt == a.k_tiles) kt = 0, ++strip;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- consumers
+    // KN: acc[r][c].x is the sum, .y unused.  NK: .x / .y are the partial sums over even / odd k, fed by
+    // packed FMAs whose operand pairs (x[k],x[k+1]) and (w[k],w[k+1]) come straight out of 128-bit loads.
+    const int kq = warp & 7, half_n = warp >> 3;  // this warp's k-quad and column half of every tile
+    float2 acc[MT][2];
+#pragma unroll
+    for (int r = 0; r < MT; ++r)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) acc[r][c] = make_float2(0.0f, 0.0f);
+    bool ok = true;
+    int strip = static_cast<int>(t_begin / a.k_tiles);
+    int kt = static_cast<int>(t_begin - static_cast<int64_t>(strip) * a.k_tiles);
+    const int first_strip = strip;
+    const int n_tiles = static_cast<int>(t_end - t_begin);
+    for (int q = 0; q < n_tiles; ++q) {
+      const int s = q % kTileStages;
+      if (ok && !mbar_wait(full + s, (q / kTileStages) & 1)) {
+        ok = false;
+        atomicOr(&g_gemv_fault, 2u);
+      }
+      if (ok) {
+        const unsigned char* tile = ring + s * kStageBytes;
+        const float* xs = reinterpret_cast<const float*>(tile + kTileWBytes);  // [MT][32]
+        float wv[4][2];  // [k e][column c]
+        if (NK) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int nloc = half_n * 64 + lane + 32 * c;
+            const float4 v = *reinterpret_cast<const float4*>(tile + nloc * 128 + ((kq ^ (nloc & 7)) << 4));
+            wv[0][c] = v.x, wv[1][c] = v.y, wv[2][c] = v.z, wv[3][c] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 v = *reinterpret_cast<const float2*>(tile + (4 * kq + e) * (kTileN * 4) + half_n * 256 + lane * 8);
+            wv[e][0] = v.x, wv[e][1] = v.y;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < MT; ++r) {
+          const float4 t = *reinterpret_cast<const float4*>(xs + r * kTileK + 4 * kq);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            if (NK) {  // packed FMAs: .x / .y accumulate the even / odd k
+              ffma2(acc[r][c], make_float2(t.x, t.y), make_float2(wv[0][c], wv[1][c]));
+              ffma2(acc[r][c], make_float2(t.z, t.w), make_float2(wv[2][c], wv[3][c]));
+            } else {
+              acc[r][c].x = fmaf(t.x, wv[0][c], acc[r][c].x);
+              acc[r][c].x = fmaf(t.y, wv[1][c], acc[r][c].x);
+              acc[r][c].x = fmaf(t.z, wv[2][c], acc[r][c].x);
+              acc[r][c].x = fmaf(t.w, wv[3][c], acc[r][c].x);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+      }
+      // ---- end of this CTA's share of the strip: fold the eight warps' sums and emit
+      if (kt == a.k_tiles - 1 || q == n_tiles - 1) {
+        const int64_t strip_first = static_cast<int64_t>(strip) * a.k_tiles;
+        const bool whole = t_begin <= strip_first && t_end >= strip_first + a.k_tiles;
+        const int slot = strip == first_strip ? 0 : 1;
+        float* spill = a.scratch + (static_cast<size_t>(blockIdx.x) * 2 + slot) * MT * kTileN;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int r = 0; r < RH; ++r)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const int cl = half_n * 64 + (NK ? lane + 32 * c : lane * 2 + c);  // column inside the strip
+              const float2 v = acc[half * RH + r][c];
+              red[(kq * RH + r) * kTileN + cl] = NK ? v.x + v.y : v.x;
+              acc[half * RH + r][c] = make_float2(0.0f, 0.0f);
+            }
+          consumer_sync();
+          for (int o = threadIdx.x; o < RH * kTileN; o += kTileConsumers * 32) {
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) v += red[w * RH * kTileN + o];
+            const int r = half * RH + o / kTileN, col = strip * kTileN + (o % kTileN);
+            if (!whole) {
+              spill[r * kTileN + (o % kTileN)] = v;
+            } else if (r < a.m && col < a.n) {
+              if (a.bias) v += a.bias[col];
+              a.y[static_cast<size_t>(r) * a.n + col] = v;
+            }
+          }
+          consumer_sync();  // red is reused by the next round / strip
+        }
+      }
+      if (++kt == a.k_tiles) kt = 0, ++strip;
+    }
+  }
+}
+
+// Adds, in CTA order, the partial sums of every strip that a range boundary cut.
+template <int MT>
+__global__ void __launch_bounds__(256)
+gemv_stream_finish_kernel(TileArgs a) {
+  const int strip = blockIdx.x;
+  const int64_t total = static_cast<int64_t>(a.strips) * a.k_tiles;
+  const int64_t first = static_cast<int64_t>(strip) * a.k_tiles, last = first + a.k_tiles;  // tile range of the strip
+  // CTAs whose ranges overlap [first, last)
+  int c_lo = static_cast<int>(first * a.ctas / total);
+  while (c_lo > 0 && tile_begin(c_lo, total, a.ctas) > first) --c_lo;
+  while (tile_begin(c_lo + 1, total, a.ctas) <= first) ++c_lo;
+  int c_hi = c_lo;
+  while (c_hi + 1 < a.ctas && tile_begin(c_hi + 1, total, a.ctas) < last) ++c_hi;
+  if (c_lo == c_hi) return;  // the strip lay inside one CTA's range; that CTA wrote y itself
+  // where each contributor parked its partial: slot 0 if this strip is the first of its range, else 1
+  __shared__ const float* src[320];
+  const int n_src = min(c_hi - c_lo + 1, 320);
+  for (int i = threadIdx.x; i < n_src; i += 256) {
+    const int c = c_lo + i;
+    const int slot = strip == static_cast<int>(tile_begin(c, total, a.ctas) / a.k_tiles) ? 0 : 1;
+    src[i] = a.scratch + (static_cast<size_t>(c) * 2 + slot) * MT * kTileN;
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < MT * kTileN; o += 256) {
+    float v = 0.0f;
+    for (int i = 0; i < n_src; ++i) v += src[i][o];
+    const int r = o / kTileN, col = strip * kTileN + (o - r * kTileN);
+    if (r < a.m && col < a.n) {
+      if (a.bias) v += a.bias[col];
+      a.y[static_cast<size_t>(r) * a.n + col] = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // host side
 
 template <int MT, int BNCOLS> constexpr size_t smem_bytes() { return (2 * MT * kChunk + MT * BNCOLS) * sizeof(float); }
@@ -368,11 +598,60 @@ int dispatch_mt(const GemvArgs& a, bool nk, int splits, bool wide, bool wvec, bo
 #undef XDK_GO
 }
 
+template <int MT>
+int launch_tile_stream(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, bool nk,
+                       float* scratch, cudaStream_t stream) {
+  TileArgs a;
+  a.bias = bias, a.y = y, a.scratch = scratch;
+  a.m = m, a.k = k, a.n = n;
+  a.strips = (n + kTileN - 1) / kTileN;
+  a.k_tiles = (k + kTileK - 1) / kTileK;
+  const int64_t total = static_cast<int64_t>(a.strips) * a.k_tiles;
+  const int64_t resident = static_cast<int64_t>(sm_count()) * kTileCtasPerSm;
+  a.ctas = static_cast<int>(total < resident ? total : resident);
+  CUtensorMap wmap, xmap;
+  {
+    const cuuint64_t dims_kn[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k)};
+    const cuuint64_t dims_nk[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(n)};
+    const cuuint64_t stride_kn[1] = {static_cast<cuuint64_t>(n) * 4}, stride_nk[1] = {static_cast<cuuint64_t>(k) * 4};
+    const cuuint32_t box_kn[2] = {kTileN, kTileK}, box_nk[2] = {kTileK, kTileN};
+    const bool ok = nk ? encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, w, dims_nk, stride_nk, box_nk, true)
+                       : encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, w, dims_kn, stride_kn, box_kn, false);
+    const cuuint64_t xdims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
+    const cuuint64_t xstride[1] = {static_cast<cuuint64_t>(k) * 4};
+    const cuuint32_t xbox[2] = {kTileK, MT};
+    if (!ok || !encode_tiled_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, x, xdims, xstride, xbox, false)) return XDK_ERR_LAUNCH;
+  }
+  const size_t smem = static_cast<size_t>(kTileStages) * (kTileWBytes + MT * kTileK * 4) +
+                      static_cast<size_t>(8) * (MT / 2) * kTileN * 4 + 2 * kTileStages * sizeof(uint64_t);
+  int st;
+  if (nk) {
+    auto kernel = gemv_stream_kernel<MT, true>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return note_launch(err);
+    st = launch(kernel, dim3(a.ctas), dim3(kTileThreads), smem, stream, 1u, a, wmap, xmap);
+  } else {
+    auto kernel = gemv_stream_kernel<MT, false>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return note_launch(err);
+    st = launch(kernel, dim3(a.ctas), dim3(kTileThreads), smem, stream, 1u, a, wmap, xmap);
+  }
+  if (st != XDK_OK) return st;
+  return launch(gemv_stream_finish_kernel<MT>, dim3(a.strips), dim3(256), 0, stream, 1u, a);
+}
+
 }  // namespace
 }  // namespace xdk
 
+extern "C" size_t xdk_gemv_scratch_bytes(int64_t m, int64_t k, int64_t n, int weight_is_nk) {
+  (void)weight_is_nk;
+  if (m <= 4 || m > 16 || k <= 0 || n <= 0) return 0;
+  const int mt = m > 8 ? 16 : 8;
+  return static_cast<size_t>(xdk::sm_count()) * xdk::kTileCtasPerSm * 2 * mt * xdk::kTileN * sizeof(float);
+}
+
 extern "C" int xdk_gemv_f32(const float* x, const float* w, const float* bias, float* y, int64_t m, int64_t k,
-                            int64_t n, int weight_is_nk, int split_k, void* stream) {
+                            int64_t n, int weight_is_nk, int split_k, void* scratch, size_t scratch_bytes, void* stream) {
   using namespace xdk;
   if (!x || !w || !y) return XDK_ERR_ARG;
   if (m <= 0 || k <= 0 || n <= 0) return XDK_ERR_ARG;
@@ -381,6 +660,18 @@ extern "C" int xdk_gemv_f32(const float* x, const float* w, const float* bias, f
   if (int st = require_sm100()) return st;
   const bool nk = weight_is_nk != 0;
 
+  // 4 < M <= 16, a large weight matrix (the two extra launch/finish microseconds pay off from about
+  // 48M elements), a scratch buffer and TMA-addressable operands: balanced persistent tile stream.
+  if (split_k == 0 && m > 4 && m <= 16 && k * n >= (48LL << 20) && scratch && scratch_bytes >= xdk_gemv_scratch_bytes(m, k, n, weight_is_nk) &&
+      aligned16(x) && aligned16(w) && aligned16(scratch) && k % 4 == 0 && (nk || n % 4 == 0) && k < (1 << 30) &&
+      n < (1 << 30)) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return m > 8 ? launch_tile_stream<16>(x, w, bias, y, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
+                                          static_cast<float*>(scratch), s)
+                 : launch_tile_stream<8>(x, w, bias, y, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
+                                         static_cast<float*>(scratch), s);
+  }
+
   // Column strip width decides the grid: prefer the wide strip (128-bit loads in KN) whenever it
   // still yields enough CTAs to cover the machine; split-K multiplies the CTA count.
   const int mt = m >= 16 ? 16 : static_cast<int>(m);
@@ -388,8 +679,14 @@ extern "C" int xdk_gemv_f32(const float* x, const float* w, const float* bias, f
   const int64_t strips_wide = (n + bn_wide - 1) / bn_wide;
   int splits = split_k;
   if (splits == 0) {
+    // Smallest split that puts about 1.5 CTAs on every SM (2.7 for the light M <= 2 KN kernel), as long
+    // as the whole grid is resident at once: a second wave costs more than any split gains.
+    const int ctas_per_sm = mt <= 2 ? 4 : (mt <= 4 ? 3 : 2);  // register-limited residency of the MT variants
+    const int64_t slots = 148LL * ctas_per_sm;
+    const int64_t want = (!nk && mt <= 2) ? 400 : 222;
     splits = 1;
-    while (splits < 8 && strips_wide * splits < 2 * 148 && k / (splits * 2) >= 256) splits *= 2;
+    while (splits < 8 && strips_wide * splits < want && strips_wide * splits * 2 <= slots && k / (splits * 2) >= 256)
+      splits *= 2;
   }
   const bool wide = nk || strips_wide * splits >= 96;
   const int64_t strips = wide ? strips_wide : (n + 31) / 32;

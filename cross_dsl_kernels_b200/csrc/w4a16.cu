@@ -19,7 +19,6 @@
 // Split-K slices of one column strip form a thread-block cluster and are summed in slice order
 // through distributed shared memory (one launch, no scratch, deterministic).
 #include <cooperative_groups.h>
-#include <cuda.h>
 
 #include "common.cuh"
 
@@ -442,28 +441,6 @@ w4a16_stream_kernel(W4Args a, StreamPlan plan, const __grid_constant__ CUtensorM
   }
 }
 
-// cuTensorMapEncodeTiled comes from the driver; fetch it through the runtime so that the library
-// needs no link-time dependency on libcuda.
-bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t* dims,
-                     const cuuint64_t* strides_bytes, const cuuint32_t* box) {
-  using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static Encode encode = nullptr;
-  if (!encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) {
-      (void)cudaGetLastError();
-      return false;
-    }
-    encode = reinterpret_cast<Encode>(fn);
-  }
-  const cuuint32_t elem_strides[2] = {1, 1};
-  return encode(map, type, 2, const_cast<void*>(base), dims, strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <bool ROWS16>
 int launch_stream(const W4Args& a, cudaStream_t stream) {
   static int sm_count = 0;
@@ -485,13 +462,13 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k / 8), static_cast<cuuint64_t>(a.n)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k / 2)};
     const cuuint32_t box[2] = {kChunkK / 8, 8};
-    if (!encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.packed, dims, strides, box)) return XDK_ERR_LAUNCH;
+    if (!encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.packed, dims, strides, box, false)) return XDK_ERR_LAUNCH;
     smap = wmap;
     if (plan.ring_scales) {
       const cuuint64_t sdims[2] = {static_cast<cuuint64_t>(a.groups), static_cast<cuuint64_t>(a.n)};
       const cuuint64_t sstrides[1] = {static_cast<cuuint64_t>(a.groups) * 2};
       const cuuint32_t sbox[2] = {static_cast<cuuint32_t>(kChunkK / a.group), 8};
-      if (!encode_tiled_2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, sdims, sstrides, sbox)) return XDK_ERR_LAUNCH;
+      if (!encode_tiled_2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, sdims, sstrides, sbox, false)) return XDK_ERR_LAUNCH;
     }
   }
   auto kernel = w4a16_stream_kernel<ROWS16>;

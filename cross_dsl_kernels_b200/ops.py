@@ -89,8 +89,14 @@ def decode_linear(x, weight, bias=None, *, out_dtype=None, weight_layout: str = 
         bias_ptr = bias.data_ptr()
     with torch.cuda.device(x.device):
         y = torch.empty((m, n), device=x.device, dtype=torch.float32)
-        status = _native.lib().xdk_gemv_f32(x.data_ptr(), weight.data_ptr(), bias_ptr, y.data_ptr(),
-                                            m, k, n, int(nk), split_k, _native.stream_ptr(x.device))
+        lib = _native.lib()
+        # Scratch for the balanced tile-stream path (4 < M <= 16, split_k = 0).  A fresh block from
+        # torch's caching allocator per call: stream-ordered, so overlapping calls never share it,
+        # and under graph capture it lives in the graph's private pool.
+        need = lib.xdk_gemv_scratch_bytes(m, k, n, int(nk)) if split_k == 0 else 0
+        scratch = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
+        status = lib.xdk_gemv_f32(x.data_ptr(), weight.data_ptr(), bias_ptr, y.data_ptr(), m, k, n, int(nk), split_k,
+                                  scratch.data_ptr() if need else None, need, _native.stream_ptr(x.device))
     _native.check(status, "xdk_gemv_f32")
     return y
 

@@ -74,7 +74,11 @@ XDK_API int xdk_rmsnorm(const void* x, const void* residual, const void* weight,
  * split_k in {1,2,4,8}: K is cut into split_k contiguous ranges (length
  * ceil(K/split_k) rounded up to a multiple of 32) that are reduced in a fixed
  * order inside one launch (thread-block cluster, distributed shared memory);
- * bias is added once, after the reduction.  split_k = 0 lets the library pick.
+ * bias is added once, after the reduction.  split_k = 0 lets the library pick; for 4 < M <= 16 it
+ * then runs a persistent tile-stream kernel that deals the weight tiles evenly to all SMs and needs
+ * `scratch` (device memory, >= xdk_gemv_scratch_bytes(...), 16-byte aligned, written and read inside
+ * the call only -- no initialisation, no state).  scratch may be NULL: the cluster kernels are used.
+ * Calls that share one scratch buffer must not overlap on the GPU.
  * Results are deterministic for a given (shape, split_k).  FP32 FMA
  * accumulation, no TF32.  bias may be NULL.  M, K, N >= 1; M > 16 is processed
  * in row tiles of 16 (the weight stream repeats per tile).
@@ -84,7 +88,10 @@ XDK_API int xdk_rmsnorm(const void* x, const void* residual, const void* weight,
  * src/crossdsl_kernels/triton/gemv_rows.py:47-146.
  */
 XDK_API int xdk_gemv_f32(const float* x, const float* w, const float* bias, float* y,
-                 int64_t m, int64_t k, int64_t n, int weight_is_nk, int split_k, void* stream);
+                 int64_t m, int64_t k, int64_t n, int weight_is_nk, int split_k,
+                 void* scratch, size_t scratch_bytes, void* stream);
+/* Bytes of scratch xdk_gemv_f32 wants for this shape on the current device (0: none needed). */
+XDK_API size_t xdk_gemv_scratch_bytes(int64_t m, int64_t k, int64_t n, int weight_is_nk);
 
 /*
  * Fused rotary embedding + paged K/V cache append, one launch.

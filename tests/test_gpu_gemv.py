@@ -86,6 +86,20 @@ def test_unaligned_views(layout):
     gate(y, x, w_kn, b, k)
 
 
+@pytest.mark.parametrize("layout", ["KN", "NK"])
+@pytest.mark.parametrize("m,k,n", [(16, 4096, 14336), (8, 4096, 14336), (5, 4100, 12300), (9, 2052, 24580), (16, 8192, 6148)])
+def test_tile_stream_path(layout, m, k, n):
+    """4 < M <= 16 on large matrices takes the persistent tile-stream kernel (scratch + finish kernel);
+    sizes off the 32 x 128 tile grid exercise the zero-filled edges."""
+    from cross_dsl_kernels_b200.ops import decode_linear
+    x, w, b, w_kn = make(m, k, n, layout, True, seed=n)
+    xd, wd, bd = x.cuda(), w.cuda(), b.cuda()
+    y = decode_linear(xd, wd, bd, weight_layout=layout)
+    gate(y, x, w_kn, b, k)
+    assert torch.equal(y, decode_linear(xd, wd, bd, weight_layout=layout)), "deterministic"
+    gate(decode_linear(xd, wd, None, weight_layout=layout), x, w_kn, None, k)
+
+
 def test_linearity_at_full_size():
     """y(a*x1 + x2) == a*y(x1) + y(x2) up to rounding: a size-independent property."""
     from cross_dsl_kernels_b200.ops import decode_linear
