@@ -643,6 +643,67 @@ int launch_tile_stream(const float* x, const float* w, const float* bias, float*
 }  // namespace
 }  // namespace xdk
 
+namespace xdk {
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// Scratch that lives in the library image instead of in caller-allocated memory.  Some hosts of
+// this library cannot hand a kernel a workspace: a serving process that gave its whole device-memory
+// budget to the KV cache at start-up and runs its decode loop with allocation switched off, or a
+// plugin interface that passes inputs and outputs only.  For them xdk_gemv_f32_static_scratch runs the
+// tile-stream kernel with its per-CTA partial sums parked in this array.  Every GPU that loads the
+// library holds the 2.5 MB until the process exits.
+constexpr int kStaticScratchCtas = 160;  // one CTA per SM; B200 has 148 SMs
+constexpr size_t kStaticScratchFloats = static_cast<size_t>(kStaticScratchCtas) * 2 * 16 * kTileN;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+// In host code the name above is only a stand-in for the symbol; the address a kernel can use has to
+// be asked for, per device, with that device current.
+float* static_scratch_for_current_device(int* status) {
+  static float* address[64];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    *status = XDK_ERR_ARCH;
+    return nullptr;
+  }
+  if (!address[dev]) {
+    float* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (err != cudaSuccess || !ptr) {
+      *status = note_launch(err == cudaSuccess ? cudaErrorInvalidSymbol : err);
+      return nullptr;
+    }
+    address[dev] = ptr;
+  }
+  *status = XDK_OK;
+  return address[dev];
+}
+
+}  // namespace
+}  // namespace xdk
+
+extern "C" int xdk_gemv_f32_static_scratch(const float* x, const float* w, const float* bias, float* y, int64_t m,
+                                           int64_t k, int64_t n, int weight_is_nk, void* stream) {
+  using namespace xdk;
+  if (!x || !w || !y) return XDK_ERR_ARG;
+  if (m <= 4 || m > 16 || k <= 0 || n <= 0) return XDK_ERR_ARG;  // the tile-stream kernel covers 4 < M <= 16
+  if (k >= (1 << 30) || n >= (1 << 30)) return XDK_ERR_LIMIT;
+  const bool nk = weight_is_nk != 0;
+  if (!aligned16(x) || !aligned16(w) || k % 4 != 0 || (!nk && n % 4 != 0)) return XDK_ERR_ARG;  // TMA-addressable operands
+  if (int st = require_sm100()) return st;
+  // the built-in array must hold two partial strips per CTA of this device
+  if (xdk_gemv_scratch_bytes(m, k, n, weight_is_nk) > kStaticScratchFloats * sizeof(float)) return XDK_ERR_LIMIT;
+  int st = XDK_OK;
+  float* scratch = static_scratch_for_current_device(&st);
+  if (!scratch) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return m > 8 ? launch_tile_stream<16>(x, w, bias, y, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
+                                        scratch, s)
+               : launch_tile_stream<8>(x, w, bias, y, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
+                                       scratch, s);
+}
+
 extern "C" size_t xdk_gemv_scratch_bytes(int64_t m, int64_t k, int64_t n, int weight_is_nk) {
   (void)weight_is_nk;
   if (m <= 4 || m > 16 || k <= 0 || n <= 0) return 0;

@@ -94,6 +94,24 @@ XDK_API int xdk_gemv_f32(const float* x, const float* w, const float* bias, floa
 XDK_API size_t xdk_gemv_scratch_bytes(int64_t m, int64_t k, int64_t n, int weight_is_nk);
 
 /*
+ * The same projection for hosts that cannot give a kernel any workspace (no counterpart in the
+ * reference).  Meant for callers that may not allocate device memory around the call -- a serving
+ * loop whose memory budget went to the KV cache at start-up, a plugin interface that passes inputs
+ * and outputs only.  It runs the tile-stream kernel of xdk_gemv_f32 (so 4 < M <= 16, 16-byte aligned
+ * x and w, K % 4 == 0 and, for KN weights, N % 4 == 0; anything else is XDK_ERR_ARG) with its partial
+ * sums in a 2.5 MB array built into the library (one copy per GPU that loads the library, held until
+ * the process exits).  The array covers devices of up to 160 SMs; a device that would need more gets
+ * XDK_ERR_LIMIT.  Nothing is allocated or freed: no cudaMalloc, no cudaFree, no allocating library
+ * call.  The first call on a device looks the array's device address up (cudaGetSymbolAddress, with
+ * that device current); make that first call before starting any stream capture.  All calls share the
+ * array.  It needs no clearing -- every slot a call reads was written earlier in the same call --
+ * but two calls that overlap on the GPU (different streams) race on it: serialise them.
+ * Results are bit-identical to xdk_gemv_f32 with split_k = 0 and a caller-provided scratch.
+ */
+XDK_API int xdk_gemv_f32_static_scratch(const float* x, const float* w, const float* bias, float* y,
+                                        int64_t m, int64_t k, int64_t n, int weight_is_nk, void* stream);
+
+/*
  * Fused rotary embedding + paged K/V cache append, one launch.
  * q [tokens,q_heads,head_dim], k,v [tokens,kv_heads,head_dim]; consecutive tokens of q, k, v are
  * {q,k,v}_token_stride elements apart (heads*head_dim when contiguous; larger when the three are
