@@ -92,6 +92,34 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// Sum NV per-lane values across the warp with a reduce-scatter (recursive halving): about NV
+// shuffles instead of 5*NV.  On return element i of lane l is the warp total of original index
+//   (l >> (5 - steps)) * (NV >> steps) + i,   steps = min(5, log2(NV)),
+// and lanes that differ only in their low (5 - steps) bits hold identical copies.
+template <int NV> __device__ __forceinline__ void warp_reduce_scatter(float (&v)[NV]) {
+  static_assert((NV & (NV - 1)) == 0, "power of two");
+  const int lane = threadIdx.x & 31;
+  int cnt = NV;
+#pragma unroll
+  for (int mask = 16; mask > 0; mask >>= 1) {
+    if (cnt > 1) {
+      const int half = cnt / 2;
+      const bool upper = (lane & mask) != 0;
+#pragma unroll
+      for (int i = 0; i < NV / 2; ++i) {
+        if (i < half) {
+          const float send = upper ? v[i] : v[i + half];
+          const float keep = upper ? v[i + half] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+        }
+      }
+      cnt = half;
+    } else {
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], mask);
+    }
+  }
+}
+
 // Element <-> float conversions used by the kernels that are generic over storage type.
 template <typename T> struct Elem;
 template <> struct Elem<float> {

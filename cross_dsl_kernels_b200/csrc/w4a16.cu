@@ -197,7 +197,8 @@ constexpr int kChunkK = 1024;                       // k per chunk
 constexpr int kRowStride = kChunkK / 2;             // a tile is a dense TMA box: 8 column rows x 512 B
 constexpr int kSlotBytes = 8 * kRowStride + 512;    // + up to 8 x 64 B of scales (dense box, 8 rows)
 // ring slots per warp: all but one hold tiles in flight; 16 staged x rows leave room for 3, 8 rows for 4
-template <bool ROWS16> struct StreamDepth { static constexpr int value = ROWS16 ? 3 : 4; };
+// MR = rows of x staged per chunk (8 for M <= 8, else 16)
+template <int MR> struct StreamDepth { static constexpr int value = MR == 16 ? 3 : 4; };
 constexpr int kMaxNB = 8;                           // column blocks per warp per pass
 
 __device__ unsigned int g_w4_fault;  // set when a bounded wait gives up
@@ -219,14 +220,15 @@ __device__ __forceinline__ void tma_box_2d(void* dst_smem, const CUtensorMap* ma
       : "memory");
 }
 
-template <bool ROWS16>
+template <int MR>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 w4a16_stream_kernel(W4Args a, StreamPlan plan, const __grid_constant__ CUtensorMap wmap,
                     const __grid_constant__ CUtensorMap smap) {
-  constexpr int kRows = ROWS16 ? 16 : 8;
+  constexpr bool ROWS16 = MR == 16;
+  constexpr int kRows = MR;
   constexpr int kXUnits = kChunkK / 8;  // 16-byte units per staged x row
   constexpr int kPassBlocks = kStreamWarps * kMaxNB;
-  constexpr int kDepth = StreamDepth<ROWS16>::value;
+  constexpr int kDepth = StreamDepth<MR>::value;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, j = lane & 3;
@@ -292,19 +294,20 @@ w4a16_stream_kernel(W4Args a, StreamPlan plan, const __grid_constant__ CUtensorM
     // staged at once; the next chunk is staged two units at a time around the tiles of the current
     // one (loads issued before a tile, permuted and stored after it) so that only two units are
     // ever live in registers during the unpack/mma loop.
-    constexpr int kStage = kRows * kXUnits / kStreamThreads;  // units per thread per chunk
+    constexpr int kStage = (kRows * kXUnits + kStreamThreads - 1) / kStreamThreads;  // units per thread per chunk
     auto x_load = [&](int kc, int i) -> U4 {
       const int idx = threadIdx.x + i * kStreamThreads;
       const int r = idx / kXUnits, u = idx - r * kXUnits;
       const int k0 = kc * kChunkK + u * 8;
       U4 v = U4{0u, 0u, 0u, 0u};
-      if (r < a.m && k0 < a.k) v = ld_cached16(a.x + static_cast<size_t>(r) * a.k + k0);
+      if (idx < kRows * kXUnits && r < a.m && k0 < a.k) v = ld_cached16(a.x + static_cast<size_t>(r) * a.k + k0);
       return v;
     };
     auto x_store = [&](int buf, int i, const U4& t) {
       const int idx = threadIdx.x + i * kStreamThreads;
+      if (idx >= kRows * kXUnits) return;
       const int r = idx / kXUnits, u = idx - r * kXUnits;
-      U4 v;
+      U4 v;  // the unpack's k order (0,4,1,5,2,6,3,7) inside every 8-block
       v.x = __byte_perm(t.x, t.z, 0x5410);
       v.y = __byte_perm(t.x, t.z, 0x7632);
       v.z = __byte_perm(t.y, t.w, 0x5410);
@@ -334,78 +337,80 @@ w4a16_stream_kernel(W4Args a, StreamPlan plan, const __grid_constant__ CUtensorM
           nx0 = x_load(kc + plan.splits, staged);
           nx1 = x_load(kc + plan.splits, staged + 1);
         }
-        const int col = (blk_begin + p0 + b) * 8 + g;
-        // Slow path only (scales not in the ring): this lane's scale for every step, fetched before the wait
-        __half sc[8];
-        if (!plan.ring_scales) {
-#pragma unroll
-          for (int st = 0; st < 8; ++st) {
-            sc[st] = __float2half(0.0f);
-            if (st < steps && col < a.n)
-              sc[st] = __ldg(a.scales + static_cast<size_t>(col) * a.groups + ((kc * kChunkK + st * 128 + j * 32) >> scale_shift));
-          }
-        }
-        pf_issue();  // refill the slot freed by the previous tile
-        const bool landed = mbar_wait(full + q % kDepth, (q / kDepth) & 1);
-        const unsigned char* slot = ring + (q % kDepth) * kSlotBytes;
-        const unsigned char* tile = slot + g * kRowStride + j * 16;
-        const __half* tile_scales =
-            reinterpret_cast<const __half*>(slot + 8 * kRowStride + g * ((kChunkK >> scale_shift) * 2));
-        if (!landed) atomicOr(&g_w4_fault, 1u);
-        float part4[8][4];  // eight independent accumulator chains hide the mma latency
-#pragma unroll
-        for (int w = 0; w < 8; ++w)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) part4[w][e] = 0.0f;
-#pragma unroll
-        for (int st = 0; st < 8; ++st) {
-          if (st >= steps || !landed) break;
-          U4 wv = U4{0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};
-          __half s1 = __float2half(0.0f);
-          if (col < a.n) {
-            wv = *reinterpret_cast<const U4*>(tile + st * 64);
-            s1 = plan.ring_scales ? tile_scales[(st * 128 + j * 32) >> scale_shift] : sc[st];
-          }
-          const __half2 s2 = __half2half2(s1);
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const int unit = st * 16 + j * 4 + w;
-            const U4 xa = xb[g * kXUnits + xunit(unit, g)];
-            U4 xc = U4{0u, 0u, 0u, 0u};
-            if constexpr (ROWS16) xc = xb[(g + 8) * kXUnits + xunit(unit, g + 8)];
-            const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
-            __half2 h[4];
-            dequant8(word, s2, h);
-            mma16816(part4[2 * w], xa.x, xc.x, xa.y, xc.y, *reinterpret_cast<uint32_t*>(&h[0]),
-                     *reinterpret_cast<uint32_t*>(&h[1]));
-            mma16816(part4[2 * w + 1], xa.z, xc.z, xa.w, xc.w, *reinterpret_cast<uint32_t*>(&h[2]),
-                     *reinterpret_cast<uint32_t*>(&h[3]));
-          }
-        }
-        __syncwarp();  // every lane is done reading the slot before the next pf_issue overwrites it
-
-        // C[row g][2j], C[g][2j+1], C[g+8][2j], C[g+8][2j+1] of this block for this chunk
-        float c4[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          c4[e] = ((part4[0][e] + part4[1][e]) + (part4[2][e] + part4[3][e])) + ((part4[4][e] + part4[5][e]) + (part4[6][e] + part4[7][e]));
-        float* mine = part + g * cols + b * 8 + 2 * j;  // rows g and g+8 of part[16][cols]; only this lane touches them
-        if (ci > 0) {
-          c4[0] += mine[0], c4[1] += mine[1];
-          c4[2] += mine[8 * cols], c4[3] += mine[8 * cols + 1];
-        }
-        if (last && plan.splits == 1) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int row = g + (e >> 1) * 8, oc = (blk_begin + p0 + b) * 8 + 2 * j + (e & 1);
-            if (row < a.m && oc < a.n) {
-              const float bv = a.bias ? __half2float(a.bias[oc]) : 0.0f;
-              a.y[static_cast<size_t>(row) * a.n + oc] = __float2half_rn(c4[e] + bv);
+        {
+          const int col = (blk_begin + p0 + b) * 8 + g;
+          // Slow path only (scales not in the ring): this lane's scale for every step, fetched before the wait
+          __half sc[8];
+          if (!plan.ring_scales) {
+  #pragma unroll
+            for (int st = 0; st < 8; ++st) {
+              sc[st] = __float2half(0.0f);
+              if (st < steps && col < a.n)
+                sc[st] = __ldg(a.scales + static_cast<size_t>(col) * a.groups + ((kc * kChunkK + st * 128 + j * 32) >> scale_shift));
             }
           }
-        } else {
-          mine[0] = c4[0], mine[1] = c4[1];
-          mine[8 * cols] = c4[2], mine[8 * cols + 1] = c4[3];
+          pf_issue();  // refill the slot freed by the previous tile
+          const bool landed = mbar_wait(full + q % kDepth, (q / kDepth) & 1);
+          const unsigned char* slot = ring + (q % kDepth) * kSlotBytes;
+          const unsigned char* tile = slot + g * kRowStride + j * 16;
+          const __half* tile_scales =
+              reinterpret_cast<const __half*>(slot + 8 * kRowStride + g * ((kChunkK >> scale_shift) * 2));
+          if (!landed) atomicOr(&g_w4_fault, 1u);
+          float part4[8][4];  // eight independent accumulator chains hide the mma latency
+  #pragma unroll
+          for (int w = 0; w < 8; ++w)
+  #pragma unroll
+            for (int e = 0; e < 4; ++e) part4[w][e] = 0.0f;
+  #pragma unroll
+          for (int st = 0; st < 8; ++st) {
+            if (st >= steps || !landed) break;
+            U4 wv = U4{0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};
+            __half s1 = __float2half(0.0f);
+            if (col < a.n) {
+              wv = *reinterpret_cast<const U4*>(tile + st * 64);
+              s1 = plan.ring_scales ? tile_scales[(st * 128 + j * 32) >> scale_shift] : sc[st];
+            }
+            const __half2 s2 = __half2half2(s1);
+  #pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const int unit = st * 16 + j * 4 + w;
+              const U4 xa = xb[g * kXUnits + xunit(unit, g)];
+              U4 xc = U4{0u, 0u, 0u, 0u};
+              if constexpr (ROWS16) xc = xb[(g + 8) * kXUnits + xunit(unit, g + 8)];
+              const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
+              __half2 h[4];
+              dequant8(word, s2, h);
+              mma16816(part4[2 * w], xa.x, xc.x, xa.y, xc.y, *reinterpret_cast<uint32_t*>(&h[0]),
+                       *reinterpret_cast<uint32_t*>(&h[1]));
+              mma16816(part4[2 * w + 1], xa.z, xc.z, xa.w, xc.w, *reinterpret_cast<uint32_t*>(&h[2]),
+                       *reinterpret_cast<uint32_t*>(&h[3]));
+            }
+          }
+          __syncwarp();  // every lane is done reading the slot before the next pf_issue overwrites it
+
+          // C[row g][2j], C[g][2j+1], C[g+8][2j], C[g+8][2j+1] of this block for this chunk
+          float c4[4];
+  #pragma unroll
+          for (int e = 0; e < 4; ++e)
+            c4[e] = ((part4[0][e] + part4[1][e]) + (part4[2][e] + part4[3][e])) + ((part4[4][e] + part4[5][e]) + (part4[6][e] + part4[7][e]));
+          float* mine = part + g * cols + b * 8 + 2 * j;  // rows g and g+8 of part[16][cols]; only this lane touches them
+          if (ci > 0) {
+            c4[0] += mine[0], c4[1] += mine[1];
+            c4[2] += mine[8 * cols], c4[3] += mine[8 * cols + 1];
+          }
+          if (last && plan.splits == 1) {
+  #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int row = g + (e >> 1) * 8, oc = (blk_begin + p0 + b) * 8 + 2 * j + (e & 1);
+              if (row < a.m && oc < a.n) {
+                const float bv = a.bias ? __half2float(a.bias[oc]) : 0.0f;
+                a.y[static_cast<size_t>(row) * a.n + oc] = __float2half_rn(c4[e] + bv);
+              }
+            }
+          } else {
+            mine[0] = c4[0], mine[1] = c4[1];
+            mine[8 * cols] = c4[2], mine[8 * cols + 1] = c4[3];
+          }
         }
         if (stage_now) {
           x_store((ci + 1) & 1, staged, nx0);
@@ -441,7 +446,7 @@ w4a16_stream_kernel(W4Args a, StreamPlan plan, const __grid_constant__ CUtensorM
   }
 }
 
-template <bool ROWS16>
+template <int MR>
 int launch_stream(const W4Args& a, cudaStream_t stream) {
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -453,8 +458,8 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
   plan.total_blocks = (a.n + 7) / 8;
   plan.chunks = (a.k + kChunkK - 1) / kChunkK;
   plan.ring_scales = (a.group <= 128 && a.k % kChunkK == 0 && aligned16(a.scales)) ? 1 : 0;
-  constexpr int kDepth = StreamDepth<ROWS16>::value;
-  const size_t smem = static_cast<size_t>(kStreamWarps) * kDepth * kSlotBytes + 2 * (ROWS16 ? 16 : 8) * kChunkK * 2 +
+  constexpr int kDepth = StreamDepth<MR>::value;
+  const size_t smem = static_cast<size_t>(kStreamWarps) * kDepth * kSlotBytes + 2 * MR * kChunkK * 2 +
                       16 * kStreamWarps * kMaxNB * 8 * sizeof(float) + kStreamWarps * kDepth * sizeof(uint64_t);
   CUtensorMap wmap, smap;
   {
@@ -471,7 +476,7 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
       if (!encode_tiled_2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, sdims, sstrides, sbox, false)) return XDK_ERR_LAUNCH;
     }
   }
-  auto kernel = w4a16_stream_kernel<ROWS16>;
+  auto kernel = w4a16_stream_kernel<MR>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return note_launch(err);
   cudaLaunchConfig_t cfg = {};
@@ -567,7 +572,7 @@ int launch_simt(W4Args a, cudaStream_t stream) {
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return note_launch(err);
   a.col_groups = (a.n + kWarps * CW - 1) / (kWarps * CW);
-  const int max_ctas = 2 * 148;
+  const int max_ctas = 4 * 148;
   a.groups_per_cta = (a.col_groups + max_ctas - 1) / max_ctas;
   const int ctas = (a.col_groups + a.groups_per_cta - 1) / a.groups_per_cta;
   return launch(kernel, dim3(ctas), dim3(kThreads), smem, stream, 1u, a);
@@ -597,9 +602,7 @@ extern "C" int xdk_w4a16(const void* x, const uint8_t* packed, const void* scale
   a.col_groups = a.groups_per_cta = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool fast = k % 32 == 0 && aligned16(packed) && aligned16(x) && m * k * 2 <= 200 * 1024;
-  if (fast && k % 128 == 0 && m >= 3) {
-    return m > 8 ? launch_stream<true>(a, s) : launch_stream<false>(a, s);
-  }
+  if (fast && k % 128 == 0 && m >= 3) return m > 8 ? launch_stream<16>(a, s) : launch_stream<8>(a, s);
   if (fast) {
     if (m == 1) return launch_simt<1, 2>(a, s);
     if (m == 2) return launch_simt<2, 2>(a, s);
