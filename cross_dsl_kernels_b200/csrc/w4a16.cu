@@ -19,6 +19,7 @@
 // Split-K slices of one column strip form a thread-block cluster and are summed in slice order
 // through distributed shared memory (one launch, no scratch, deterministic).
 #include <cooperative_groups.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -535,6 +536,318 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
 }
 
 
+// ------------------------------------------------------------------------------------------------
+// tcgen05 path (M > 8, K % 512 == 0, group >= 64): the contraction runs on the 5th-generation tensor
+// cores.  Operands are swapped so that the UMMA "M" dimension is a strip of up to 128 output columns:
+//     D[128 columns x 16 tokens] += A[128 x 16 k] * B[16 k x 16],   A = dequantised W,  B = x^T
+// One persistent CTA per SM owns a contiguous, evenly dealt range of 8-column blocks and walks it
+// in strips of <= 128 columns, full K each (no split-K, no cross-CTA reduction).
+//   warp 8, one lane : TMA box copies of the packed codes of a (strip, 512-k chunk) -- one 2 KB box per
+//                      8-column block -- into a double-buffered shared-memory area, plus the strip's scales
+//   warps 0-7        : stage x for the chunk (k order of the unpack, canonical K-major core-matrix layout),
+//                      then unpack 128-k stages of the strip into the A operand buffer in the same canonical
+//                      layout (8 rows x 16 bytes per core matrix), fence to the async proxy, arrive
+//   warp 9, one lane : per stage 8 x tcgen05.mma (K = 16) accumulating in TMEM, tcgen05.commit onto the
+//                      barriers that hand the stage / x buffer back and announce the finished strip
+//   warps 0-3        : epilogue -- tcgen05.ld of the 128 x 16 FP32 accumulator, bias, FP16 store
+// Every wait is time-bounded; on a timeout the kernel raises g_w4_fault, stops issuing work, and still
+// frees its TMEM columns before it returns.
+constexpr int kUChunkK = 256;                  // k per packed chunk
+constexpr int kUPackedBufs = 4;                // packed chunks in flight (16 KB each at 128 columns)
+constexpr int kUStageK = 128;                  // k per unpack/MMA stage
+constexpr int kUStages = 3;                    // A operand buffers
+constexpr int kULbo = 128;                     // bytes between k-adjacent core matrices of A
+constexpr int kUSbo = (kUStageK / 8) * kULbo;  // bytes between 8-row groups of A
+constexpr int kUABytes = 16 * kUSbo;           // one A stage: 16 row groups
+constexpr int kUXLbo = 128, kUXSbo = (kUChunkK / 8) * kUXLbo;  // x chunk: [2 row groups][64 k groups][8 x 16 B]
+constexpr int kUXBytes = 2 * kUXSbo;
+constexpr int kUPackedBytes = 16 * 8 * (kUChunkK / 2);  // packed codes of a 128-column strip chunk
+constexpr int kUThreads = 10 * 32;
+
+struct UmmaPlan {
+  int ctas, total_blocks, chunks;
+  int scale_row_bytes;  // bytes of scales per column (groups * 2)
+};
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, int lbo, int sbo) {
+  return static_cast<uint64_t>((smem_addr >> 4) & 0x3fff) | (static_cast<uint64_t>((lbo >> 4) & 0x3fff) << 16) |
+         (static_cast<uint64_t>((sbo >> 4) & 0x3fff) << 32) | (1ull << 46);  // version 1, no swizzle
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(kUThreads, 1)
+w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* packed = smem_raw;                                   // [kUPackedBufs][kUPackedBytes]
+  unsigned char* abuf = packed + kUPackedBufs * kUPackedBytes;                   // [kUStages][kUABytes]
+  unsigned char* xbuf = abuf + kUStages * kUABytes;                   // [2][kUXBytes]
+  unsigned char* scbuf = xbuf + 2 * kUXBytes;                         // [16 blocks][8 cols][scale_row_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(scbuf + 16 * 8 * plan.scale_row_bytes);
+  uint64_t* pk_full = bars;                       // [kUPackedBufs]  TMA bytes of a packed chunk landed
+  uint64_t* pk_empty = bars + kUPackedBufs;       // [kUPackedBufs]  the 8 unpack warps are done with the chunk
+  uint64_t* a_full = bars + 2 * kUPackedBufs;     // [kUStages] the 8 unpack warps wrote the stage
+  uint64_t* a_empty = a_full + kUStages;          // [kUStages] MMAs that read the stage completed (commit)
+  uint64_t* x_full = a_empty + kUStages;          // [2]
+  uint64_t* x_empty = x_full + 2;                // [2]
+  uint64_t* sc_full = x_empty + 2;               // [1]
+  uint64_t* acc_full = sc_full + 1;              // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int blk_begin = static_cast<int>(static_cast<int64_t>(blockIdx.x) * plan.total_blocks / plan.ctas);
+  const int blk_end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * plan.total_blocks / plan.ctas);
+  const int scale_shift = 31 - __clz(a.group);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kUPackedBufs; ++i) {
+      mbar_init(pk_full + i, 1);
+      mbar_init(pk_empty + i, 8);   // one arrival per unpack warp
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(x_full + i, 8);
+      mbar_init(x_empty + i, 1);
+    }
+    for (int i = 0; i < kUStages; ++i) {
+      mbar_init(a_full + i, 8);
+      mbar_init(a_empty + i, 1);
+    }
+    mbar_init(sc_full, 1);
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 9) {  // TMEM: 32 columns (the minimum), one 128 x 16 FP32 accumulator is used
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 32;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int q = 0, strip_i = 0;  // chunk counter over the CTA's life, strip counter
+      bool ok = true;
+      for (int b0 = blk_begin; b0 < blk_end && ok; b0 += 16, ++strip_i) {
+        const int nb = min(16, blk_end - b0);
+        // scales of the strip (whole K): wait until the previous strip's readers are done = its last chunk buffer was released
+        if (strip_i > 0) {
+          const int prev = q - 1;  // last chunk of the previous strip
+          ok = mbar_wait(pk_empty + prev % kUPackedBufs, (prev / kUPackedBufs) & 1);
+          if (!ok) break;
+        }
+        mbar_expect_tx(sc_full, static_cast<unsigned>(nb * 8 * plan.scale_row_bytes));
+        for (int b = 0; b < nb; ++b) tma_box_2d(scbuf + b * 8 * plan.scale_row_bytes, &smap, 0, (b0 + b) * 8, sc_full);
+        for (int kc = 0; kc < plan.chunks; ++kc, ++q) {
+          const int buf = q % kUPackedBufs;
+          if (q >= kUPackedBufs && !mbar_wait(pk_empty + buf, ((q / kUPackedBufs) - 1) & 1)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(pk_full + buf, static_cast<unsigned>(nb * 8 * (kUChunkK / 2)));
+          for (int b = 0; b < nb; ++b)
+            tma_box_2d(packed + buf * kUPackedBytes + b * 8 * (kUChunkK / 2), &wmap, kc * (kUChunkK / 8), (b0 + b) * 8, pk_full + buf);
+        }
+      }
+      if (!ok) atomicOr(&g_w4_fault, 4u);
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t kIdesc = (1u << 4) | (2u << 17) | (8u << 24);  // D = F32, A = B = F16 K-major, N = 16, M = 128
+      int q = 0, sq = 0;  // chunk counter, stage counter
+      bool ok = true;
+      for (int b0 = blk_begin; b0 < blk_end && ok; b0 += 16) {
+        for (int kc = 0; kc < plan.chunks && ok; ++kc, ++q) {
+          const int xb = q & 1;
+          ok = mbar_wait(x_full + xb, (q >> 1) & 1);
+          for (int st = 0; st < kUChunkK / kUStageK && ok; ++st, ++sq) {
+            const int s = sq % kUStages;
+            ok = mbar_wait(a_full + s, (sq / kUStages) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_base = smem_u32(abuf + s * kUABytes);
+            const uint32_t x_base = smem_u32(xbuf + xb * kUXBytes) + st * (kUStageK / 8) * kUXLbo;
+#pragma unroll
+            for (int j = 0; j < kUStageK / 16; ++j)
+              umma_f16(tmem_acc, umma_desc(a_base + j * 2 * kULbo, kULbo, kUSbo), umma_desc(x_base + j * 2 * kUXLbo, kUXLbo, kUXSbo),
+                       kIdesc, !(kc == 0 && st == 0 && j == 0));
+            umma_commit(a_empty + s);  // the stage buffer is free once these MMAs have read it
+          }
+          if (ok) umma_commit(x_empty + xb);
+        }
+        if (ok) umma_commit(acc_full);
+      }
+      if (!ok) atomicOr(&g_w4_fault, 8u);
+    }
+  } else {
+    // ------------------------------------------------------------ unpack warps (+ x staging, epilogue)
+    const int t = threadIdx.x;  // 0 .. 255
+    int q = 0, sq = 0, strip_i = 0;
+    bool ok = true;
+    U4 xin[2];  // this thread's two 16-byte units of the next x chunk
+    auto load_x = [&](int kc) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int idx = t + i * 256;
+        const int m = idx >> 5, kg = idx & 31;
+        xin[i] = U4{0u, 0u, 0u, 0u};
+        if (m < a.m) xin[i] = ld_cached16(a.x + static_cast<size_t>(m) * a.k + kc * kUChunkK + kg * 8);
+      }
+    };
+    load_x(0);
+    for (int b0 = blk_begin; b0 < blk_end; b0 += 16, ++strip_i) {
+      const int nb = min(16, blk_end - b0);
+      const int ncols = nb * 8;
+      if (ok) ok = mbar_wait(sc_full, strip_i & 1);
+      for (int kc = 0; kc < plan.chunks; ++kc, ++q) {
+        const int buf = q % kUPackedBufs, xb = q & 1;
+        // ---- x chunk -> canonical K-major layout, k order of the unpack inside each 8-block.  The global
+        // loads for this chunk were issued one chunk earlier (xin), so only the stores sit on the path.
+        if (ok && q >= 2) ok = mbar_wait(x_empty + xb, ((q >> 1) - 1) & 1);
+        if (ok) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int idx = t + i * 256;  // 16 rows x 32 k groups
+            const int m = idx >> 5, kg = idx & 31;
+            U4 v;
+            v.x = __byte_perm(xin[i].x, xin[i].z, 0x5410);
+            v.y = __byte_perm(xin[i].x, xin[i].z, 0x7632);
+            v.z = __byte_perm(xin[i].y, xin[i].w, 0x5410);
+            v.w = __byte_perm(xin[i].y, xin[i].w, 0x7632);
+            *reinterpret_cast<U4*>(xbuf + xb * kUXBytes + (m >> 3) * kUXSbo + kg * kUXLbo + (m & 7) * 16) = v;
+          }
+          fence_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cta(x_full + xb);
+        load_x(kc + 1 < plan.chunks ? kc + 1 : 0);  // next chunk (x does not depend on the strip)
+        // ---- packed chunk -> A stages
+        if (ok) ok = mbar_wait(pk_full + buf, (q / kUPackedBufs) & 1);
+        for (int st = 0; st < kUChunkK / kUStageK; ++st, ++sq) {
+          const int s = sq % kUStages;
+          if (ok && sq >= kUStages) ok = mbar_wait(a_empty + s, ((sq / kUStages) - 1) & 1);
+          if (ok) {
+            tc_fence_after();
+            unsigned char* astage = abuf + s * kUABytes;
+            constexpr int kQuarters = kUStageK / 32;  // 16-byte loads (32 codes) per column and stage
+#pragma unroll
+            for (int i = 0; i < 128 * kQuarters / 256; ++i) {
+              const int item = t + i * 256;
+              const int c = item & 127, qd = item >> 7;  // consecutive lanes: consecutive columns = rows of one core matrix
+              if (c < ncols) {
+                // packed tiles arrive 128-byte swizzled: 16-byte piece p of row r sits at piece p ^ (r & 7), so the
+                // eight lanes that read the same piece of eight different rows hit eight different bank groups
+                const unsigned char* row = packed + buf * kUPackedBytes + (c >> 3) * 8 * (kUChunkK / 2) + (c & 7) * (kUChunkK / 2);
+                const int piece = st * (kUStageK / 32) + qd;
+                const U4 wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));
+                const int k_local = kc * kUChunkK + st * kUStageK + qd * 32;
+                const __half s1 = reinterpret_cast<const __half*>(scbuf + ((c >> 3) * 8 + (c & 7)) * plan.scale_row_bytes)[k_local >> scale_shift];
+                const __half2 s2 = __half2half2(s1);
+                unsigned char* dst = astage + (c >> 3) * kUSbo + (c & 7) * 16 + (qd * 4) * kULbo;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                  const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
+                  __half2 h[4];
+                  dequant8(word, s2, h);
+                  U4 o;
+                  o.x = *reinterpret_cast<uint32_t*>(&h[0]);
+                  o.y = *reinterpret_cast<uint32_t*>(&h[1]);
+                  o.z = *reinterpret_cast<uint32_t*>(&h[2]);
+                  o.w = *reinterpret_cast<uint32_t*>(&h[3]);
+                  *reinterpret_cast<U4*>(dst + w * kULbo) = o;
+                }
+              }
+            }
+            fence_async_smem();
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cta(a_full + s);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cta(pk_empty + buf);
+      }
+      // ---- epilogue of the strip: warps 0-3 read TMEM lanes 32*warp .. +31 = columns of the strip
+      if (warp < 4) {
+        if (ok) ok = mbar_wait(acc_full, strip_i & 1);
+        if (ok) {
+          tc_fence_after();
+          uint32_t r[16];
+          const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+              : "r"(taddr));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int c = warp * 32 + lane, col = b0 * 8 + c;
+          if (c < ncols && col < a.n) {
+            const float bv = a.bias ? __half2float(a.bias[col]) : 0.0f;
+#pragma unroll
+            for (int m = 0; m < 16; ++m)
+              if (m < a.m) a.y[static_cast<size_t>(m) * a.n + col] = __float2half_rn(__uint_as_float(r[m]) + bv);
+          }
+          tc_fence_before();
+        }
+      }
+      // all 256 threads meet before the next strip's stages can reach the MMA warp (its a_full needs all of them),
+      // so the next strip's first MMA cannot overwrite TMEM while it is still being read
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
+    if (!ok && lane == 0) atomicOr(&g_w4_fault, 16u);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 32;" ::"r"(tmem_acc) : "memory");
+  }
+}
+
+int launch_umma(const W4Args& a, cudaStream_t stream) {
+  UmmaPlan plan;
+  plan.total_blocks = (a.n + 7) / 8;
+  plan.ctas = plan.total_blocks < sm_count() ? plan.total_blocks : sm_count();
+  plan.chunks = a.k / kUChunkK;
+  plan.scale_row_bytes = a.groups * 2;
+  const size_t smem = kUPackedBufs * kUPackedBytes + kUStages * kUABytes + 2 * kUXBytes + 16 * 8 * plan.scale_row_bytes + 32 * sizeof(uint64_t);
+  if (smem > 220 * 1024) return XDK_ERR_LIMIT;
+  CUtensorMap wmap, smap;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k / 8), static_cast<cuuint64_t>(a.n)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k / 2)};
+    const cuuint32_t box[2] = {kUChunkK / 8, 8};
+    const cuuint64_t sdims[2] = {static_cast<cuuint64_t>(a.groups), static_cast<cuuint64_t>(a.n)};
+    const cuuint64_t sstrides[1] = {static_cast<cuuint64_t>(a.groups) * 2};
+    const cuuint32_t sbox[2] = {static_cast<cuuint32_t>(a.groups), 8};
+    static_assert(kUChunkK / 2 == 128, "the packed box is one 128-byte swizzle span wide");
+    if (!encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.packed, dims, strides, box, true) ||
+        !encode_tiled_2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, sdims, sstrides, sbox, false))
+      return XDK_ERR_LAUNCH;
+  }
+  cudaError_t err = cudaFuncSetAttribute(w4a16_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (err != cudaSuccess) return note_launch(err);
+  return launch(w4a16_umma_kernel, dim3(plan.ctas), dim3(kUThreads), smem, stream, 1u, a, plan, wmap, smap);
+}
+
 // Any K (odd included), any alignment: warp per column, lane per byte (two codes), rows one at a
 // time.  Slow; it exists so that every shape the format allows has a GPU path.
 __global__ void __launch_bounds__(kThreads)
@@ -602,6 +915,12 @@ extern "C" int xdk_w4a16(const void* x, const uint8_t* packed, const void* scale
   a.col_groups = a.groups_per_cta = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool fast = k % 32 == 0 && aligned16(packed) && aligned16(x) && m * k * 2 <= 200 * 1024;
+  // XDK_W4A16_UMMA=1 opts in to the tcgen05 kernel while it is being validated
+  static const bool use_umma = getenv("XDK_W4A16_UMMA") && getenv("XDK_W4A16_UMMA")[0] == '1';
+  if (use_umma && fast && m > 8 && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales)) {
+    const int st = launch_umma(a, s);
+    if (st != XDK_ERR_LIMIT) return st;
+  }
   if (fast && k % 128 == 0 && m >= 3) return m > 8 ? launch_stream<16>(a, s) : launch_stream<8>(a, s);
   if (fast) {
     if (m == 1) return launch_simt<1, 2>(a, s);

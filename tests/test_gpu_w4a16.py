@@ -128,3 +128,33 @@ def test_rejections():
     for call in bad:
         with pytest.raises((ValueError, RuntimeError)):
             call()
+
+
+def test_tcgen05_path_matches_oracle_in_a_fresh_process():
+    """The opt-in tcgen05 kernel (XDK_W4A16_UMMA=1, read once per process) is checked in a child
+    process: TMEM accumulator, UMMA descriptors and the canonical shared-memory layouts must give the
+    oracle's values for full and ragged strips, small and large M > 8."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    from conftest import ROOT
+    code = textwrap.dedent("""
+        import sys, torch
+        sys.path.insert(0, %r)
+        from cross_dsl_kernels_b200 import workloads as wl
+        from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+        from oracle import int4
+        for (m, k, n, g, bias) in [(16, 256, 8, 128, False), (9, 1024, 200, 64, True), (16, 4096, 4096, 128, False),
+                                   (12, 2048, 1001 * 8, 256, True), (16, 4096, 28672, 128, False)]:
+            x, packed, scales, b = wl.w4a16_inputs(m, k, n, g, bias, seed=n + m)
+            y = w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), b.cuda() if bias else None, group_size=g)
+            ref = int4.w4a16_projection(x, packed, scales, b, group_size=g)
+            err = (y.cpu().double() - ref.double()).abs()
+            assert bool((err <= 0.002 + 0.002 * ref.double().abs()).all()), (m, k, n, g, float(err.max()))
+            assert float((y.cpu().double() - ref.double()).norm() / ref.double().norm()) <= 1e-3
+        print("umma ok")
+    """ % str(ROOT))
+    env = dict(os.environ, XDK_W4A16_UMMA="1")
+    done = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0 and "umma ok" in done.stdout, done.stdout + done.stderr
