@@ -42,6 +42,7 @@ ROOT = pathlib.Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+T0 = time.perf_counter()
 K = 4096
 SWEEP = [(m, n, layout) for m in (1, 4, 16) for layout in ("KN", "NK") for n in (4096, 14336)]
 METRIC = "achieved HBM GB/s of the FP32 decode-projection sweep (algorithmic bytes / CUDA-graph step time)"
@@ -132,16 +133,24 @@ def workload_config(gpus: int) -> dict:
 # GPU arm
 
 
-def build_gpu_sweep(rank: int, world: int):
-    """Device tensors for this rank's column shard of every projection."""
-    from cross_dsl_kernels_b200 import workloads as wl
+def mark(text: str) -> None:
+    """Progress line on stderr (rank, seconds since start): shows where a multi-rank run spends its time."""
+    sys.stderr.write(f"[bench rank {os.environ.get('RANK', '0')} +{time.perf_counter() - T0:6.1f}s] {text}\n")
+    sys.stderr.flush()
 
+
+def build_gpu_sweep(rank: int, world: int):
+    """Device tensors for this rank's column shard of every projection (drawn on the device: the same
+    Philox stream on every rank, so the shards are slices of one matrix)."""
     weights = {}
     for n in (4096, 14336):
-        _, w, b = wl.projection_inputs(1, K, n, "KN", True, seed=n)
+        g = torch.Generator(device="cuda").manual_seed(n)
+        w = torch.randn(K, n, generator=g, device="cuda") / K ** 0.5
+        b = 0.02 * torch.randn(n, generator=g, device="cuda")
         lo, hi = rank * n // world, (rank + 1) * n // world
-        weights[(n, "KN")] = (w[:, lo:hi].contiguous().cuda(), b[lo:hi].contiguous().cuda())
-        weights[(n, "NK")] = (w.t()[lo:hi].contiguous().cuda(), b[lo:hi].contiguous().cuda())
+        weights[(n, "KN")] = (w[:, lo:hi].contiguous(), b[lo:hi].contiguous())
+        weights[(n, "NK")] = (w.t()[lo:hi].contiguous(), b[lo:hi].contiguous())
+        del w
     xs_host = {m: torch.randn(m, K, generator=torch.Generator().manual_seed(m)).pin_memory() for m in (1, 4, 16)}
     xs = {m: t.cuda() for m, t in xs_host.items()}
     return xs_host, xs, weights
@@ -170,11 +179,25 @@ def main() -> None:
     from cross_dsl_kernels_b200.ops import decode_linear
     from cross_dsl_kernels_b200.timing import ClockSampler
 
+    # A multi-rank run that stalls (a peer that never joins, a collective that never completes) must not
+    # sit until an outer limit kills it: after the budget every rank reports where it was and leaves.
+    import signal
+
+    def _expired(signum, frame):
+        mark("watchdog: time budget exceeded, leaving")
+        os._exit(3)
+
+    signal.signal(signal.SIGALRM, _expired)
+    signal.alarm(540)
+
+    mark("start")
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        mark("process group ready")
     peaks = measured_peaks()
     xs_host, xs, weights = build_gpu_sweep(rank, world)
+    mark("sweep weights on device")
     # own kernels per step: one per projection, two (stream + finish) where the tile-stream path is taken
     launches_per_step = sum(2 if (4 < m <= 16 and K * (n // world) >= (48 << 20)) else 1 for m, n, _ in SWEEP)
 
@@ -199,9 +222,11 @@ def main() -> None:
         for _ in range(2):
             step()
     stream.synchronize()
+    mark("sweep warmed up")
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=stream):
         step()
+    mark("sweep captured")
 
     def barrier():
         if world > 1:
@@ -224,6 +249,7 @@ def main() -> None:
         while time.perf_counter() < t_end:
             graph.replay()
         torch.cuda.synchronize()
+    mark("sweep timed")
     elapsed_ms = torch.tensor([start.elapsed_time(end)], device="cuda")
     if world > 1:
         dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
@@ -269,10 +295,12 @@ def main() -> None:
                 "sweep_achieved": round(value / world, 2), "sweep_frac": round(value / world / peaks["hbm_gbs"], 4),
                 "note": "FP32-FMA-issue co-limited at M=16 (16 FMAs per weight element); M<=4 kernels reach 0.83-1.00 of the measured peak, see kernels[]"}
 
+    mark("dominant kernel timed")
     chain_row = None
     if not args.no_table:
         chain_row = kernel_bench.bench_chain(rank=rank, world=world, peak=peaks["hbm_gbs"])
 
+    mark("chain done")
     if rank != 0:
         finish(world)
         return

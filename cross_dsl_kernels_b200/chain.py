@@ -85,9 +85,11 @@ def unshard_reference(gathered: torch.Tensor) -> torch.Tensor:
 
 
 def _quantised(n: int, k: int, group: int, gen: torch.Generator):
-    codes = torch.randint(0, 16, (n, k), generator=gen)
-    packed = pack_int4((codes - 8).to(torch.int8))
-    scales = (0.005 + 0.015 * torch.rand(n, k // group, generator=gen)).half()
+    """Codes uniform in [0, 15], scales uniform in [0.005, 0.02]; drawn on the generator's device."""
+    dev = gen.device
+    codes = torch.randint(0, 16, (n, k), generator=gen, device=dev, dtype=torch.int8)
+    packed = pack_int4(codes - 8)
+    scales = (0.005 + 0.015 * torch.rand(n, k // group, generator=gen, device=dev)).half()
     return packed, scales
 
 
@@ -110,6 +112,9 @@ class DecodeLayerChain:
         self.cfg, self.rank, self.world, self.pg = cfg, rank, world, group
         self.device = torch.device(device)
         c = cfg
+        # Weights are drawn on the device (Philox, same values on every rank for one seed): drawing
+        # 4 x 140 M codes on one host thread per rank would dominate a multi-rank start-up.
+        wgen = torch.Generator(device=self.device).manual_seed(seed)
         gen = torch.Generator().manual_seed(seed)
         d = c.head_dim
         hq, hkv = c.q_heads // world, c.kv_heads // world
@@ -118,16 +123,17 @@ class DecodeLayerChain:
         for _ in range(layers):
             w1 = (1 + 0.1 * torch.randn(c.hidden, generator=gen)).half()
             w2 = (1 + 0.1 * torch.randn(c.hidden, generator=gen)).half()
-            qkv_p, qkv_s = _quantised(c.qkv_cols, c.hidden, c.group, gen)
-            up_p, up_s = _quantised(2 * c.mlp, c.hidden, c.group, gen)
-            rows = qkv_shard_rows(c, rank, world)
-            up_rows = upgate_shard_rows(c, rank, world)
-            self.layers.append(dict(
+            qkv_p, qkv_s = _quantised(c.qkv_cols, c.hidden, c.group, wgen)
+            up_p, up_s = _quantised(2 * c.mlp, c.hidden, c.group, wgen)
+            rows = qkv_shard_rows(c, rank, world).to(self.device)
+            up_rows = upgate_shard_rows(c, rank, world).to(self.device)
+            layer = dict(
                 w1=w1.to(self.device), w2=w2.to(self.device),
-                qkv_packed=qkv_p[rows].contiguous().to(self.device), qkv_scales=qkv_s[rows].contiguous().to(self.device),
-                up_packed=up_p[up_rows].contiguous().to(self.device), up_scales=up_s[up_rows].contiguous().to(self.device),
-                host=dict(w1=w1, w2=w2, qkv_packed=qkv_p, qkv_scales=qkv_s, up_packed=up_p, up_scales=up_s, qkv_rows=rows),
-            ))
+                qkv_packed=qkv_p[rows].contiguous(), qkv_scales=qkv_s[rows].contiguous(),
+                up_packed=up_p[up_rows].contiguous(), up_scales=up_s[up_rows].contiguous())
+            if world == 1:  # full (unsharded) weights for checkers; copied to the host only when asked for
+                layer["full"] = dict(w1=w1, w2=w2, qkv_packed=qkv_p, qkv_scales=qkv_s, up_packed=up_p, up_scales=up_s)
+            self.layers.append(layer)
         pages_per_seq = c.context // c.page_size
         pages = c.tokens * pages_per_seq
         self.positions = torch.randint(0, c.context, (c.tokens,), generator=gen)
@@ -149,6 +155,10 @@ class DecodeLayerChain:
         self.q_full = torch.empty(c.tokens, c.hidden, dtype=torch.float16, device=self.device)
         self.up_full = torch.empty(c.tokens, 2 * c.mlp, dtype=torch.float16, device=self.device)
         self.launches_per_layer = 5 if world == 1 else 7
+
+    def host_weights(self, layer: int = 0) -> dict:
+        """CPU copies of one layer's unsharded weights (single-rank chains only; for checkers)."""
+        return {k: v.cpu() for k, v in self.layers[layer]["full"].items()}
 
     def step(self, layer: int = 0, h=None, res=None) -> dict:
         """One layer: returns every intermediate (device tensors)."""

@@ -26,7 +26,7 @@ def test_chain_stages_match_oracle(small):
     cfg = ChainConfig(hidden=1024, q_heads=8, kv_heads=2, mlp=1536, context=256) if small else ChainConfig()
     chain = DecodeLayerChain(cfg, layers=1)
     out = {k: v.cpu() for k, v in chain.step(0).items()}
-    host = chain.layers[0]["host"]
+    host = chain.host_weights(0)
     d, hq, hkv, t = cfg.head_dim, cfg.q_heads, cfg.kv_heads, cfg.tokens
 
     n1, r1 = decode_ops.residual_rmsnorm(chain.h, chain.res, host["w1"], cfg.eps)
