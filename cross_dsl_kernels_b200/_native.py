@@ -24,6 +24,7 @@ SIGNATURES = {
     "xdk_abi_version": (_int, []),
     "xdk_last_cuda_error": (_int, []),
     "xdk_device_supported": (_int, [_int]),
+    "xdk_fault_flags": (ctypes.c_uint, []),
     "xdk_rmsnorm": (_int, [_p, _p, _p, _p, _p, _i64, _i64, ctypes.c_float, _int, _p]),
     "xdk_gemv_f32": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, ctypes.c_size_t, _p]),
     "xdk_gemv_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _int]),
@@ -59,6 +60,11 @@ def check(status: int, what: str) -> None:
     handle = lib()
     text = handle.xdk_strerror(status).decode()
     raise NativeLibraryError(f"{what}: {text} (status {status}, cudaError {handle.xdk_last_cuda_error()})")
+
+
+def fault_flags() -> int:
+    """OR of the kernels' wait-timeout bits on the current device (0 = healthy); synchronises."""
+    return int(lib().xdk_fault_flags())
 
 
 def dtype_code(dtype) -> int:

@@ -81,6 +81,8 @@ int xdk_abi_version(void) { return XDK_ABI_VERSION; }
 
 int xdk_last_cuda_error(void) { return xdk::g_last_cuda_error; }
 
+unsigned xdk_fault_flags(void) { return xdk::gemv_fault_word() | (xdk::w4a16_fault_word() << 8); }
+
 int xdk_device_supported(int device) {
   int count = 0;
   if (cudaGetDeviceCount(&count) != cudaSuccess) {

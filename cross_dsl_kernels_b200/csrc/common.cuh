@@ -24,6 +24,9 @@ int require_sm100();
 bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t* dims,
                      const cuuint64_t* strides_bytes, const cuuint32_t* box, bool swizzle128);
 int sm_count();  // SMs of the current device (cached per device)
+// Fault words of the kernels with bounded waits (current device; synchronises).  0 = no wait ever gave up.
+unsigned gemv_fault_word();
+unsigned w4a16_fault_word();
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

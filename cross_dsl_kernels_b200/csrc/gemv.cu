@@ -676,6 +676,17 @@ extern "C" int xdk_gemv_f32_static_scratch(const float* x, const float* w, const
                                        scratch, s);
 }
 
+namespace xdk {
+unsigned gemv_fault_word() {
+  unsigned v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemv_fault, sizeof(v)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0x80000000u;
+  }
+  return v;
+}
+}  // namespace xdk
+
 extern "C" size_t xdk_gemv_scratch_bytes(int64_t m, int64_t k, int64_t n, int weight_is_nk) {
   (void)weight_is_nk;
   if (m <= 4 || m > 16 || k <= 0 || n <= 0) return 0;

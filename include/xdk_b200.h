@@ -52,6 +52,13 @@ XDK_API const char* xdk_strerror(int status);
 XDK_API int xdk_abi_version(void);
 /* cudaError_t (as int) of the most recent failed launch on this host thread, 0 if none. */
 XDK_API int xdk_last_cuda_error(void);
+/*
+ * Kernels that wait on mbarriers (the TMA-fed projection kernels) bound every wait by wall time; a wait
+ * that gives up makes the kernel skip the work, set a bit here and return normally, so a lost copy can
+ * never hang the GPU.  Returns the OR of those bits on the current device since the library was loaded
+ * (bits 0-7: FP32 projection, 8-15: W4A16); 0 means no wait ever gave up.  Synchronises the device.
+ */
+XDK_API unsigned xdk_fault_flags(void);
 /* XDK_OK when `device` exists and is compute capability 10.x, else XDK_ERR_ARCH/ARG. */
 XDK_API int xdk_device_supported(int device);
 

@@ -66,3 +66,11 @@ def test_static_scratch_rejects_what_it_cannot_hold():
     assert lib.xdk_gemv_f32_static_scratch(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), 17, 64, 128, 0, stream) == -1
     assert lib.xdk_gemv_f32_static_scratch(x.data_ptr() + 4, w.data_ptr(), None, y.data_ptr(), 8, 60, 128, 0, stream) == -1
     assert lib.xdk_gemv_f32_static_scratch(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), 8, 1 << 30, 128, 0, stream) == -4
+
+
+def test_no_device_side_wait_ever_gave_up():
+    """Runs after the whole GPU suite: none of the time-bounded mbarrier waits in the TMA-fed kernels
+    may have expired in this process."""
+    from cross_dsl_kernels_b200 import _native
+    torch.cuda.synchronize()
+    assert _native.fault_flags() == 0
