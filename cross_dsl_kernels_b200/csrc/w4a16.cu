@@ -555,7 +555,7 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
 constexpr int kUChunkK = 256;                  // k per packed chunk
 constexpr int kUPackedBufs = 4;                // packed chunks in flight (16 KB each at 128 columns)
 constexpr int kUStageK = 128;                  // k per unpack/MMA stage
-constexpr int kUStages = 4;                    // A operand buffers
+constexpr int kUStages = 3;                    // A operand buffers
 constexpr int kULbo = 128;                     // bytes between k-adjacent core matrices of A
 constexpr int kUSbo = (kUStageK / 8) * kULbo;  // bytes between 8-row groups of A
 constexpr int kUABytes = 16 * kUSbo;           // one A stage: 16 row groups
