@@ -537,32 +537,44 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
 
 
 // ------------------------------------------------------------------------------------------------
-// tcgen05 path (M > 8, K % 512 == 0, group >= 64): the contraction runs on the 5th-generation tensor
+// tcgen05 path (M > 8, K % 256 == 0, group >= 64): the contraction runs on the 5th-generation tensor
 // cores.  Operands are swapped so that the UMMA "M" dimension is a strip of up to 128 output columns:
 //     D[128 columns x 16 tokens] += A[128 x 16 k] * B[16 k x 16],   A = dequantised W,  B = x^T
+// and A lives in TENSOR MEMORY: the unpack warps write the dequantised weights straight from registers
+// into TMEM (tcgen05.st), so they never pass through shared memory.  (With A in shared memory every
+// M=128,N=16 MMA re-reads 4 KB of A for 16 columns of use, which by itself saturates the 128 B/clk
+// shared-memory port and starves the unpack warps that share it.)
 // One persistent CTA per SM owns a contiguous, evenly dealt range of 8-column blocks and walks it
 // in strips of <= 128 columns, full K each (no split-K, no cross-CTA reduction).
-//   warp 8, one lane : TMA box copies of the packed codes of a (strip, 512-k chunk) -- one 2 KB box per
-//                      8-column block -- into a double-buffered shared-memory area, plus the strip's scales
-//   warps 0-7        : stage x for the chunk (k order of the unpack, canonical K-major core-matrix layout),
-//                      then unpack 128-k stages of the strip into the A operand buffer in the same canonical
-//                      layout (8 rows x 16 bytes per core matrix), fence to the async proxy, arrive
-//   warp 9, one lane : per stage 8 x tcgen05.mma (K = 16) accumulating in TMEM, tcgen05.commit onto the
-//                      barriers that hand the stage / x buffer back and announce the finished strip
-//   warps 0-3        : epilogue -- tcgen05.ld of the 128 x 16 FP32 accumulator, bias, FP16 store
+//   warp 8, one lane : TMA box copies of the packed codes of a (strip, 256-k chunk) -- one 1 KB box per
+//                      8-column block, 128-byte swizzled -- into a ring of chunk buffers, plus the strip's scales
+//   warps 10-11      : stage x for each chunk in shared memory (k order of the unpack, canonical K-major
+//                      core-matrix layout); x is the B operand, read through a shared-memory descriptor
+//   warps 0-7        : thread = one column of the strip (TMEM lane); warp w owns lane quarter w % 4 and k half
+//                      w / 4 of every 128-k stage: 16-byte shared loads of codes -> dequant -> tcgen05.st
+//   warps 9, 12-14   : MMA issuers, one lane each.  A warp gets a tcgen05.mma out only every ~100 cycles, whatever
+//                      the shape (measured: 94-118 cycles per M=128 MMA for N = 16 .. 128), while four warps
+//                      issuing side by side reach one per ~29 cycles.  So the 8 K=16 blocks of a stage are dealt
+//                      round-robin to 4 issuers, each accumulating into its OWN 128 x 16 FP32 accumulator, then
+//                      tcgen05.commit onto the barriers (count 4) that hand the stage / x buffer back and
+//                      announce the finished strip
+//   warps 0-3        : epilogue -- tcgen05.ld of the four accumulators, summed in fixed order, bias, FP16 store
+// TMEM columns (512 allocated; the kernel is alone on its SM): 16 i .. accumulator of issuer i, 64 + 64 s .. A stage s.
 // Every wait is time-bounded; on a timeout the kernel raises g_w4_fault, stops issuing work, and still
 // frees its TMEM columns before it returns.
 constexpr int kUChunkK = 256;                  // k per packed chunk
-constexpr int kUPackedBufs = 4;                // packed chunks in flight (16 KB each at 128 columns)
+constexpr int kUPackedBufs = 8;                // packed chunks in flight (16 KB each at 128 columns)
 constexpr int kUStageK = 128;                  // k per unpack/MMA stage
-constexpr int kUStages = 3;                    // A operand buffers
-constexpr int kULbo = 128;                     // bytes between k-adjacent core matrices of A
-constexpr int kUSbo = (kUStageK / 8) * kULbo;  // bytes between 8-row groups of A
-constexpr int kUABytes = 16 * kUSbo;           // one A stage: 16 row groups
-constexpr int kUXLbo = 128, kUXSbo = (kUChunkK / 8) * kUXLbo;  // x chunk: [2 row groups][64 k groups][8 x 16 B]
+constexpr int kUStages = 6;                    // A operand stages in TMEM
+constexpr int kUTmemCols = 512;                // allocation (power of two)
+constexpr int kUTmemA = 64;                    // first column of A stage 0
+constexpr int kUStageCols = kUStageK / 2;      // 32-bit TMEM columns per stage (two FP16 k per column)
+static_assert(kUTmemA + kUStages * kUStageCols <= kUTmemCols, "A stages must fit the TMEM allocation");
+constexpr int kUXLbo = 128, kUXSbo = (kUChunkK / 8) * kUXLbo;  // x chunk: [2 row groups][32 k groups][8 x 16 B]
 constexpr int kUXBytes = 2 * kUXSbo;
 constexpr int kUPackedBytes = 16 * 8 * (kUChunkK / 2);  // packed codes of a 128-column strip chunk
-constexpr int kUThreads = 10 * 32;
+constexpr int kUIssuers = 4;                   // MMA-issuing warps, one accumulator each
+constexpr int kUThreads = 15 * 32;             // 8 unpack warps, TMA warp, MMA warp 0, 2 x-staging warps, MMA warps 1-3
 
 struct UmmaPlan {
   int ctas, total_blocks, chunks;
@@ -573,12 +585,20 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, int lbo, int s
   return static_cast<uint64_t>((smem_addr >> 4) & 0x3fff) | (static_cast<uint64_t>((lbo >> 4) & 0x3fff) << 16) |
          (static_cast<uint64_t>((sbo >> 4) & 0x3fff) << 32) | (1ull << 46);  // version 1, no swizzle
 }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+// D (TMEM) (+)= A (TMEM) * B (shared memory descriptor)
+__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -595,13 +615,12 @@ __global__ void __launch_bounds__(kUThreads, 1)
 w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* packed = smem_raw;                                   // [kUPackedBufs][kUPackedBytes]
-  unsigned char* abuf = packed + kUPackedBufs * kUPackedBytes;                   // [kUStages][kUABytes]
-  unsigned char* xbuf = abuf + kUStages * kUABytes;                   // [2][kUXBytes]
+  unsigned char* xbuf = packed + kUPackedBufs * kUPackedBytes;        // [2][kUXBytes]
   unsigned char* scbuf = xbuf + 2 * kUXBytes;                         // [16 blocks][8 cols][scale_row_bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(scbuf + 16 * 8 * plan.scale_row_bytes);
   uint64_t* pk_full = bars;                       // [kUPackedBufs]  TMA bytes of a packed chunk landed
   uint64_t* pk_empty = bars + kUPackedBufs;       // [kUPackedBufs]  the 8 unpack warps are done with the chunk
-  uint64_t* a_full = bars + 2 * kUPackedBufs;     // [kUStages] the 8 unpack warps wrote the stage
+  uint64_t* a_full = bars + 2 * kUPackedBufs;     // [kUStages] the 8 unpack warps wrote the stage to TMEM
   uint64_t* a_empty = a_full + kUStages;          // [kUStages] MMAs that read the stage completed (commit)
   uint64_t* x_full = a_empty + kUStages;          // [2]
   uint64_t* x_empty = x_full + 2;                // [2]
@@ -620,19 +639,19 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       mbar_init(pk_empty + i, 8);   // one arrival per unpack warp
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(x_full + i, 8);
-      mbar_init(x_empty + i, 1);
+      mbar_init(x_full + i, 2);   // one arrival per x-staging warp
+      mbar_init(x_empty + i, kUIssuers);
     }
     for (int i = 0; i < kUStages; ++i) {
       mbar_init(a_full + i, 8);
-      mbar_init(a_empty + i, 1);
+      mbar_init(a_empty + i, kUIssuers);
     }
     mbar_init(sc_full, 1);
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, kUIssuers);
     mbar_fence_init();
   }
-  if (warp == 9) {  // TMEM: 32 columns (the minimum), one 128 x 16 FP32 accumulator is used
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 32;" ::"r"(smem_u32(tmem_slot)) : "memory");
+  if (warp == 9) {  // TMEM: accumulator + A stages
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(kUTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -668,10 +687,15 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       }
       if (!ok) atomicOr(&g_w4_fault, 4u);
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == 9 || warp >= 12) {
+    // ------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       constexpr uint32_t kIdesc = (1u << 4) | (2u << 17) | (8u << 24);  // D = F32, A = B = F16 K-major, N = 16, M = 128
+      const int issuer = warp == 9 ? 0 : warp - 11;
+      const uint32_t acc = tmem_acc + issuer * 16;
+      // x descriptor: only the 14-bit start-address field changes from MMA to MMA
+      const uint64_t xd0 = umma_desc(smem_u32(xbuf), kUXLbo, kUXSbo);
+      const uint32_t xd_lo = static_cast<uint32_t>(xd0), xd_hi = static_cast<uint32_t>(xd0 >> 32);
       int q = 0, sq = 0;  // chunk counter, stage counter
       bool ok = true;
       for (int b0 = blk_begin; b0 < blk_end && ok; b0 += 16) {
@@ -683,13 +707,15 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
             ok = mbar_wait(a_full + s, (sq / kUStages) & 1);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t a_base = smem_u32(abuf + s * kUABytes);
-            const uint32_t x_base = smem_u32(xbuf + xb * kUXBytes) + st * (kUStageK / 8) * kUXLbo;
+            const uint32_t a_base = tmem_acc + kUTmemA + s * kUStageCols + issuer * 8;
+            const uint32_t x_lo = xd_lo + ((xb * kUXBytes + (st * (kUStageK / 8) + issuer * 2) * kUXLbo) >> 4);
 #pragma unroll
-            for (int j = 0; j < kUStageK / 16; ++j)
-              umma_f16(tmem_acc, umma_desc(a_base + j * 2 * kULbo, kULbo, kUSbo), umma_desc(x_base + j * 2 * kUXLbo, kUXLbo, kUXSbo),
-                       kIdesc, !(kc == 0 && st == 0 && j == 0));
-            umma_commit(a_empty + s);  // the stage buffer is free once these MMAs have read it
+            for (int j = 0; j < kUStageK / 16 / kUIssuers; ++j) {  // K blocks issuer, issuer + 4, ...
+              uint64_t xd;
+              asm("mov.b64 %0, {%1, %2};" : "=l"(xd) : "r"(x_lo + ((j * kUIssuers * 2 * kUXLbo) >> 4)), "r"(xd_hi));
+              umma_f16_ta(acc, a_base + j * kUIssuers * 8, xd, kIdesc, !(kc == 0 && st == 0 && j == 0));
+            }
+            umma_commit(a_empty + s);  // the TMEM stage is free once every issuer's MMAs have read it
           }
           if (ok) umma_commit(x_empty + xb);
         }
@@ -697,36 +723,33 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       }
       if (!ok) atomicOr(&g_w4_fault, 8u);
     }
-  } else {
-    // ------------------------------------------------------------ unpack warps (+ x staging, epilogue)
-    const int t = threadIdx.x;  // 0 .. 255
-    int q = 0, sq = 0, strip_i = 0;
-    bool ok = true;
-    U4 xin[2];  // this thread's two 16-byte units of the next x chunk
+  } else if (warp >= 10) {  // 10, 11
+    // ------------------------------------------------------------ x staging warps
+    // x chunk -> canonical K-major layout with the unpack's k order inside each 8-block.  The global loads
+    // of a chunk are issued one chunk ahead, so only the permute + stores sit between two hand-offs.
+    const int t = threadIdx.x - 320;  // 0 .. 63
+    U4 xin[8];
     auto load_x = [&](int kc) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int idx = t + i * 256;
-        const int m = idx >> 5, kg = idx & 31;
+      for (int i = 0; i < 8; ++i) {
+        const int idx = t + i * 64;  // 16 rows x 32 k groups; a warp covers 8 rows x 4 k groups = 512 contiguous bytes of xbuf
+        const int m = (idx & 7) | ((idx >> 8) << 3), kg = (idx >> 3) & 31;
         xin[i] = U4{0u, 0u, 0u, 0u};
         if (m < a.m) xin[i] = ld_cached16(a.x + static_cast<size_t>(m) * a.k + kc * kUChunkK + kg * 8);
       }
     };
     load_x(0);
-    for (int b0 = blk_begin; b0 < blk_end; b0 += 16, ++strip_i) {
-      const int nb = min(16, blk_end - b0);
-      const int ncols = nb * 8;
-      if (ok) ok = mbar_wait(sc_full, strip_i & 1);
+    int q = 0;
+    bool ok = true;
+    for (int b0 = blk_begin; b0 < blk_end; b0 += 16) {
       for (int kc = 0; kc < plan.chunks; ++kc, ++q) {
-        const int buf = q % kUPackedBufs, xb = q & 1;
-        // ---- x chunk -> canonical K-major layout, k order of the unpack inside each 8-block.  The global
-        // loads for this chunk were issued one chunk earlier (xin), so only the stores sit on the path.
+        const int xb = q & 1;
         if (ok && q >= 2) ok = mbar_wait(x_empty + xb, ((q >> 1) - 1) & 1);
         if (ok) {
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int idx = t + i * 256;  // 16 rows x 32 k groups
-            const int m = idx >> 5, kg = idx & 31;
+          for (int i = 0; i < 8; ++i) {
+            const int idx = t + i * 64;
+            const int m = (idx & 7) | ((idx >> 8) << 3), kg = (idx >> 3) & 31;
             U4 v;
             v.x = __byte_perm(xin[i].x, xin[i].z, 0x5410);
             v.y = __byte_perm(xin[i].x, xin[i].z, 0x7632);
@@ -739,44 +762,53 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
         __syncwarp();
         if (lane == 0) mbar_arrive_cta(x_full + xb);
         load_x(kc + 1 < plan.chunks ? kc + 1 : 0);  // next chunk (x does not depend on the strip)
-        // ---- packed chunk -> A stages
+      }
+    }
+    if (!ok && lane == 0) atomicOr(&g_w4_fault, 32u);
+  } else {
+    // ------------------------------------------------------------ unpack warps (+ epilogue)
+    const int lq = warp & 3, kh = warp >> 2;  // TMEM lane quarter this warp may touch, k half of a stage
+    const int c = lq * 32 + lane;             // this thread's column of the strip = its TMEM lane
+    const uint32_t a_lane_base = tmem_acc + (static_cast<uint32_t>(lq * 32) << 16) + kUTmemA + kh * (kUStageCols / 2);
+    int q = 0, sq = 0, strip_i = 0;
+    bool ok = true;
+    for (int b0 = blk_begin; b0 < blk_end; b0 += 16, ++strip_i) {
+      const int nb = min(16, blk_end - b0);
+      const int ncols = nb * 8;
+      const bool warp_live = lq * 32 < ncols;  // warp-uniform: a quarter without columns writes nothing
+      if (ok) ok = mbar_wait(sc_full, strip_i & 1);
+      const unsigned char* sc_row = scbuf + c * plan.scale_row_bytes;
+      for (int kc = 0; kc < plan.chunks; ++kc, ++q) {
+        const int buf = q % kUPackedBufs;
         if (ok) ok = mbar_wait(pk_full + buf, (q / kUPackedBufs) & 1);
+        // packed tiles arrive 128-byte swizzled: 16-byte piece p of row r sits at piece p ^ (r & 7), so the
+        // lanes of a warp, which read the same piece of 32 different rows, spread over all bank groups
+        const unsigned char* row = packed + buf * kUPackedBytes + (c >> 3) * 8 * (kUChunkK / 2) + (c & 7) * (kUChunkK / 2);
         for (int st = 0; st < kUChunkK / kUStageK; ++st, ++sq) {
           const int s = sq % kUStages;
           if (ok && sq >= kUStages) ok = mbar_wait(a_empty + s, ((sq / kUStages) - 1) & 1);
-          if (ok) {
+          if (ok && warp_live) {
             tc_fence_after();
-            unsigned char* astage = abuf + s * kUABytes;
-            constexpr int kQuarters = kUStageK / 32;  // 16-byte loads (32 codes) per column and stage
+            const int k_half = kc * kUChunkK + st * kUStageK + kh * (kUStageK / 2);  // 64 k: inside one group (group >= 64)
+            const __half2 s2 = __half2half2(reinterpret_cast<const __half*>(sc_row)[k_half >> scale_shift]);
 #pragma unroll
-            for (int i = 0; i < 128 * kQuarters / 256; ++i) {
-              const int item = t + i * 256;
-              const int c = item & 127, qd = item >> 7;  // consecutive lanes: consecutive columns = rows of one core matrix
-              if (c < ncols) {
-                // packed tiles arrive 128-byte swizzled: 16-byte piece p of row r sits at piece p ^ (r & 7), so the
-                // eight lanes that read the same piece of eight different rows hit eight different bank groups
-                const unsigned char* row = packed + buf * kUPackedBytes + (c >> 3) * 8 * (kUChunkK / 2) + (c & 7) * (kUChunkK / 2);
-                const int piece = st * (kUStageK / 32) + qd;
-                const U4 wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));
-                const int k_local = kc * kUChunkK + st * kUStageK + qd * 32;
-                const __half s1 = reinterpret_cast<const __half*>(scbuf + ((c >> 3) * 8 + (c & 7)) * plan.scale_row_bytes)[k_local >> scale_shift];
-                const __half2 s2 = __half2half2(s1);
-                unsigned char* dst = astage + (c >> 3) * kUSbo + (c & 7) * 16 + (qd * 4) * kULbo;
+            for (int pc = 0; pc < kUStageK / 64; ++pc) {
+              const int piece = st * (kUStageK / 32) + kh * (kUStageK / 64) + pc;
+              U4 wv = U4{0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};  // code 8 = weight 0 for columns past the strip
+              if (c < ncols) wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));
+              uint32_t r[16];
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                  const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
-                  __half2 h[4];
-                  dequant8(word, s2, h);
-                  U4 o;
-                  o.x = *reinterpret_cast<uint32_t*>(&h[0]);
-                  o.y = *reinterpret_cast<uint32_t*>(&h[1]);
-                  o.z = *reinterpret_cast<uint32_t*>(&h[2]);
-                  o.w = *reinterpret_cast<uint32_t*>(&h[3]);
-                  *reinterpret_cast<U4*>(dst + w * kULbo) = o;
-                }
+              for (int w = 0; w < 4; ++w) {
+                const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
+                __half2 h[4];
+                dequant8(word, s2, h);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) r[4 * w + i] = *reinterpret_cast<uint32_t*>(&h[i]);
               }
+              tmem_st16(a_lane_base + s * kUStageCols + pc * 16, r);
             }
-            fence_async_smem();
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
           }
           __syncwarp();
           if (lane == 0) mbar_arrive_cta(a_full + s);
@@ -789,20 +821,26 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
         if (ok) ok = mbar_wait(acc_full, strip_i & 1);
         if (ok) {
           tc_fence_after();
-          uint32_t r[16];
+          float sum[16];
           const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-              : "r"(taddr));
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          const int c = warp * 32 + lane, col = b0 * 8 + c;
+#pragma unroll
+          for (int i = 0; i < kUIssuers; ++i) {
+            uint32_t r[16];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                : "r"(taddr + i * 16));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int m = 0; m < 16; ++m) sum[m] = i == 0 ? __uint_as_float(r[m]) : __fadd_rn(sum[m], __uint_as_float(r[m]));
+          }
+          const int col = b0 * 8 + c;  // warps 0-3: lq == warp, so c is this thread's accumulator lane too
           if (c < ncols && col < a.n) {
             const float bv = a.bias ? __half2float(a.bias[col]) : 0.0f;
 #pragma unroll
             for (int m = 0; m < 16; ++m)
-              if (m < a.m) a.y[static_cast<size_t>(m) * a.n + col] = __float2half_rn(__uint_as_float(r[m]) + bv);
+              if (m < a.m) a.y[static_cast<size_t>(m) * a.n + col] = __float2half_rn(sum[m] + bv);
           }
           tc_fence_before();
         }
@@ -818,7 +856,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
   __syncthreads();
   if (warp == 9) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 32;" ::"r"(tmem_acc) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "n"(kUTmemCols) : "memory");
   }
 }
 
@@ -828,7 +866,7 @@ int launch_umma(const W4Args& a, cudaStream_t stream) {
   plan.ctas = plan.total_blocks < sm_count() ? plan.total_blocks : sm_count();
   plan.chunks = a.k / kUChunkK;
   plan.scale_row_bytes = a.groups * 2;
-  const size_t smem = kUPackedBufs * kUPackedBytes + kUStages * kUABytes + 2 * kUXBytes + 16 * 8 * plan.scale_row_bytes + 32 * sizeof(uint64_t);
+  const size_t smem = kUPackedBufs * kUPackedBytes + 2 * kUXBytes + 16 * 8 * plan.scale_row_bytes + 48 * sizeof(uint64_t);
   if (smem > 220 * 1024) return XDK_ERR_LIMIT;
   CUtensorMap wmap, smap;
   {
