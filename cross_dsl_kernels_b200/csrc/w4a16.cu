@@ -546,12 +546,12 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
 // shared-memory port and starves the unpack warps that share it.)
 // One persistent CTA per SM owns a contiguous, evenly dealt range of 8-column blocks and walks it
 // in strips of <= 128 columns, full K each (no split-K, no cross-CTA reduction).
-//   warp 8, one lane : TMA box copies of the packed codes of a (strip, 256-k chunk) -- one 1 KB box per
-//                      8-column block, 128-byte swizzled -- into a ring of chunk buffers, plus the strip's scales
+//   warp 8, one lane : TMA box copies of the packed codes of a (strip, 256-k chunk) -- one 4 KB box per
+//                      32 columns, 128-byte swizzled -- into a ring of chunk buffers, plus the strip's scales
 //   warps 10-11      : stage x for each chunk in shared memory (k order of the unpack, canonical K-major
 //                      core-matrix layout); x is the B operand, read through a shared-memory descriptor
 //   warps 0-7        : thread = one column of the strip (TMEM lane); warp w owns lane quarter w % 4 and k half
-//                      w / 4 of every 128-k stage: 16-byte shared loads of codes -> dequant -> tcgen05.st
+//                      w / 4 of every 256-k stage (= chunk): 16-byte shared loads of codes -> dequant -> tcgen05.st
 //   warps 9, 12-14   : MMA issuers, one lane each.  A warp gets a tcgen05.mma out only every ~100 cycles, whatever
 //                      the shape (measured: 94-118 cycles per M=128 MMA for N = 16 .. 128), while four warps
 //                      issuing side by side reach one per ~29 cycles.  So the 8 K=16 blocks of a stage are dealt
@@ -564,8 +564,8 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
 // frees its TMEM columns before it returns.
 constexpr int kUChunkK = 256;                  // k per packed chunk
 constexpr int kUPackedBufs = 8;                // packed chunks in flight (16 KB each at 128 columns)
-constexpr int kUStageK = 128;                  // k per unpack/MMA stage
-constexpr int kUStages = 6;                    // A operand stages in TMEM
+constexpr int kUStageK = 256;                  // k per unpack/MMA stage (= one packed chunk: fewer hand-offs per k)
+constexpr int kUStages = 3;                    // A operand stages in TMEM
 constexpr int kUTmemCols = 512;                // allocation (power of two)
 constexpr int kUTmemA = 64;                    // first column of A stage 0
 constexpr int kUStageCols = kUStageK / 2;      // 32-bit TMEM columns per stage (two FP16 k per column)
@@ -577,7 +577,7 @@ constexpr int kUIssuers = 4;                   // MMA-issuing warps, one accumul
 constexpr int kUThreads = 15 * 32;             // 8 unpack warps, TMA warp, MMA warp 0, 2 x-staging warps, MMA warps 1-3
 
 struct UmmaPlan {
-  int ctas, total_blocks, chunks;
+  int ctas, total_blocks, chunks;  // total_blocks counts 32-column units
   int scale_row_bytes;  // bytes of scales per column (groups * 2)
 };
 
@@ -629,8 +629,9 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int blk_begin = static_cast<int>(static_cast<int64_t>(blockIdx.x) * plan.total_blocks / plan.ctas);
-  const int blk_end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * plan.total_blocks / plan.ctas);
+  // the CTA's range of 8-column blocks, dealt in units of 4 blocks (one TMEM lane quarter, one 32-row TMA box)
+  const int blk_begin = 4 * static_cast<int>(static_cast<int64_t>(blockIdx.x) * plan.total_blocks / plan.ctas);
+  const int blk_end = 4 * static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * plan.total_blocks / plan.ctas);
   const int scale_shift = 31 - __clz(a.group);
 
   if (threadIdx.x == 0) {
@@ -673,7 +674,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
           if (!ok) break;
         }
         mbar_expect_tx(sc_full, static_cast<unsigned>(nb * 8 * plan.scale_row_bytes));
-        for (int b = 0; b < nb; ++b) tma_box_2d(scbuf + b * 8 * plan.scale_row_bytes, &smap, 0, (b0 + b) * 8, sc_full);
+        for (int b = 0; b < nb; b += 4) tma_box_2d(scbuf + b * 8 * plan.scale_row_bytes, &smap, 0, (b0 + b) * 8, sc_full);
         for (int kc = 0; kc < plan.chunks; ++kc, ++q) {
           const int buf = q % kUPackedBufs;
           if (q >= kUPackedBufs && !mbar_wait(pk_empty + buf, ((q / kUPackedBufs) - 1) & 1)) {
@@ -681,7 +682,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
             break;
           }
           mbar_expect_tx(pk_full + buf, static_cast<unsigned>(nb * 8 * (kUChunkK / 2)));
-          for (int b = 0; b < nb; ++b)
+          for (int b = 0; b < nb; b += 4)  // 32-row boxes; the 128-byte swizzle depends on (row & 7) only, so rows stay where 8-row boxes put them
             tma_box_2d(packed + buf * kUPackedBytes + b * 8 * (kUChunkK / 2), &wmap, kc * (kUChunkK / 8), (b0 + b) * 8, pk_full + buf);
         }
       }
@@ -789,10 +790,11 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
           if (ok && sq >= kUStages) ok = mbar_wait(a_empty + s, ((sq / kUStages) - 1) & 1);
           if (ok && warp_live) {
             tc_fence_after();
-            const int k_half = kc * kUChunkK + st * kUStageK + kh * (kUStageK / 2);  // 64 k: inside one group (group >= 64)
-            const __half2 s2 = __half2half2(reinterpret_cast<const __half*>(sc_row)[k_half >> scale_shift]);
+            const int k_half = kc * kUChunkK + st * kUStageK + kh * (kUStageK / 2);
 #pragma unroll
             for (int pc = 0; pc < kUStageK / 64; ++pc) {
+              // two pieces = 64 k lie inside one group (group >= 64)
+              const __half2 s2 = __half2half2(reinterpret_cast<const __half*>(sc_row)[(k_half + (pc & ~1) * 32) >> scale_shift]);
               const int piece = st * (kUStageK / 32) + kh * (kUStageK / 64) + pc;
               U4 wv = U4{0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};  // code 8 = weight 0 for columns past the strip
               if (c < ncols) wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));
@@ -862,7 +864,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
 
 int launch_umma(const W4Args& a, cudaStream_t stream) {
   UmmaPlan plan;
-  plan.total_blocks = (a.n + 7) / 8;
+  plan.total_blocks = (a.n + 31) / 32;  // units of 32 columns
   plan.ctas = plan.total_blocks < sm_count() ? plan.total_blocks : sm_count();
   plan.chunks = a.k / kUChunkK;
   plan.scale_row_bytes = a.groups * 2;
@@ -872,10 +874,10 @@ int launch_umma(const W4Args& a, cudaStream_t stream) {
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k / 8), static_cast<cuuint64_t>(a.n)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k / 2)};
-    const cuuint32_t box[2] = {kUChunkK / 8, 8};
+    const cuuint32_t box[2] = {kUChunkK / 8, 32};
     const cuuint64_t sdims[2] = {static_cast<cuuint64_t>(a.groups), static_cast<cuuint64_t>(a.n)};
     const cuuint64_t sstrides[1] = {static_cast<cuuint64_t>(a.groups) * 2};
-    const cuuint32_t sbox[2] = {static_cast<cuuint32_t>(a.groups), 8};
+    const cuuint32_t sbox[2] = {static_cast<cuuint32_t>(a.groups), 32};
     static_assert(kUChunkK / 2 == 128, "the packed box is one 128-byte swizzle span wide");
     if (!encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.packed, dims, strides, box, true) ||
         !encode_tiled_2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, sdims, sstrides, sbox, false))
@@ -964,9 +966,13 @@ extern "C" int xdk_w4a16(const void* x, const uint8_t* packed, const void* scale
   a.col_groups = a.groups_per_cta = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool fast = k % 32 == 0 && aligned16(packed) && aligned16(x) && m * k * 2 <= 200 * 1024;
-  // XDK_W4A16_UMMA=1 opts in to the tcgen05 kernel while it is being validated
-  static const bool use_umma = getenv("XDK_W4A16_UMMA") && getenv("XDK_W4A16_UMMA")[0] == '1';
-  if (use_umma && fast && m > 8 && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales)) {
+  // tcgen05 kernel: taken where every SM gets at least two 32-column units (measured at K = 4096, M = 16:
+  // 18.6 vs 26.0 us at N = 14336, 32.8 vs 42.4 us at N = 28672, but 16.1 vs 12.5 us at N = 4096, where only one
+  // TMEM lane quarter per SM has columns to unpack).  XDK_W4A16_UMMA=1 / =0 forces it on (where eligible) / off.
+  static const int umma_env = getenv("XDK_W4A16_UMMA") ? (getenv("XDK_W4A16_UMMA")[0] == '1' ? 1 : 0) : -1;
+  const bool umma_ok = fast && m > 8 && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales);
+  const bool use_umma = umma_env >= 0 ? umma_env == 1 : n >= 64LL * sm_count();
+  if (use_umma && umma_ok) {
     const int st = launch_umma(a, s);
     if (st != XDK_ERR_LIMIT) return st;
   }

@@ -130,10 +130,12 @@ def test_rejections():
             call()
 
 
-def test_tcgen05_path_matches_oracle_in_a_fresh_process():
-    """The opt-in tcgen05 kernel (XDK_W4A16_UMMA=1, read once per process) is checked in a child
-    process: TMEM accumulator, UMMA descriptors and the canonical shared-memory layouts must give the
-    oracle's values for full and ragged strips, small and large M > 8."""
+@pytest.mark.parametrize("force", ["1", "0"])
+def test_both_m16_paths_match_oracle_in_a_fresh_process(force):
+    """The library picks the tcgen05 kernel for wide projections and the mma.sync kernel for narrow ones;
+    XDK_W4A16_UMMA (read once per process) forces one of them, so each is checked over the same narrow,
+    ragged and wide shapes in a child process.  For the tcgen05 kernel this covers the TMEM-resident A
+    operand, the UMMA descriptors of x, the four accumulators and full, ragged and multiple strips."""
     import os
     import subprocess
     import sys
@@ -153,8 +155,10 @@ def test_tcgen05_path_matches_oracle_in_a_fresh_process():
             err = (y.cpu().double() - ref.double()).abs()
             assert bool((err <= 0.002 + 0.002 * ref.double().abs()).all()), (m, k, n, g, float(err.max()))
             assert float((y.cpu().double() - ref.double()).norm() / ref.double().norm()) <= 1e-3
+        from cross_dsl_kernels_b200 import _native
+        assert _native.fault_flags() == 0
         print("umma ok")
     """ % str(ROOT))
-    env = dict(os.environ, XDK_W4A16_UMMA="1")
+    env = dict(os.environ, XDK_W4A16_UMMA=force)
     done = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0 and "umma ok" in done.stdout, done.stdout + done.stderr
