@@ -29,8 +29,8 @@ int require_sm100() {
   return major == 10 ? XDK_OK : XDK_ERR_ARCH;
 }
 
-bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t* dims,
-                     const cuuint64_t* strides_bytes, const cuuint32_t* box, bool swizzle128) {
+bool encode_tiled(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
+                  const cuuint64_t* strides_bytes, const cuuint32_t* box, bool swizzle128) {
   using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -44,10 +44,16 @@ bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* bas
     }
     encode = reinterpret_cast<Encode>(fn);
   }
-  const cuuint32_t elem_strides[2] = {1, 1};
-  return encode(map, type, 2, const_cast<void*>(base), dims, strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  if (rank < 1 || rank > 5) return false;
+  return encode(map, type, static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims, strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t* dims,
+                     const cuuint64_t* strides_bytes, const cuuint32_t* box, bool swizzle128) {
+  return encode_tiled(map, type, 2, base, dims, strides_bytes, box, swizzle128);
 }
 
 int sm_count() {

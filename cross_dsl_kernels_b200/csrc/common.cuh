@@ -18,9 +18,12 @@ int note_launch(cudaError_t err);
 // XDK_OK when the device current to this thread is compute capability 10.x (cached per device).
 int require_sm100();
 
-// Encodes a 2-D tiled TMA tensor map (dims/box innermost first, strides in bytes for dim 1).
-// cuTensorMapEncodeTiled is fetched from the driver through the runtime, so the library has no
-// link-time dependency on libcuda.  swizzle128: 128-byte swizzle (inner box must be 128 bytes).
+// Encodes a tiled TMA tensor map of `rank` dimensions (dims/box: rank entries, innermost first;
+// strides_bytes: rank - 1 entries, for dims 1 ..).  cuTensorMapEncodeTiled is fetched from the driver
+// through the runtime, so the library has no link-time dependency on libcuda.  swizzle128: 128-byte
+// swizzle (inner box must be 128 bytes).  encode_tiled_2d is the rank-2 shorthand.
+bool encode_tiled(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
+                  const cuuint64_t* strides_bytes, const cuuint32_t* box, bool swizzle128);
 bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t* dims,
                      const cuuint64_t* strides_bytes, const cuuint32_t* box, bool swizzle128);
 int sm_count();  // SMs of the current device (cached per device)

@@ -468,13 +468,13 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k / 8), static_cast<cuuint64_t>(a.n)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k / 2)};
     const cuuint32_t box[2] = {kChunkK / 8, 8};
-    if (!encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.packed, dims, strides, box, false)) return XDK_ERR_LAUNCH;
+    if (!encode_tiled(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a.packed, dims, strides, box, false)) return XDK_ERR_LAUNCH;
     smap = wmap;
     if (plan.ring_scales) {
       const cuuint64_t sdims[2] = {static_cast<cuuint64_t>(a.groups), static_cast<cuuint64_t>(a.n)};
       const cuuint64_t sstrides[1] = {static_cast<cuuint64_t>(a.groups) * 2};
       const cuuint32_t sbox[2] = {static_cast<cuuint32_t>(kChunkK / a.group), 8};
-      if (!encode_tiled_2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, sdims, sstrides, sbox, false)) return XDK_ERR_LAUNCH;
+      if (!encode_tiled(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.scales, sdims, sstrides, sbox, false)) return XDK_ERR_LAUNCH;
     }
   }
   auto kernel = w4a16_stream_kernel<MR>;
@@ -538,48 +538,69 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
 
 // ------------------------------------------------------------------------------------------------
 // tcgen05 path (M > 8, K % 256 == 0, group >= 64): the contraction runs on the 5th-generation tensor
-// cores.  Operands are swapped so that the UMMA "M" dimension is a strip of up to 128 output columns:
-//     D[128 columns x 16 tokens] += A[128 x 16 k] * B[16 k x 16],   A = dequantised W,  B = x^T
+// cores.  Operands are swapped so that the UMMA "M" dimension (128 TMEM lanes) carries output columns:
+//     D[128 lanes x 16 S] += A[128 x 16 k] * B[16 k x 16 S],   A = dequantised W,  B = x^T
 // and A lives in TENSOR MEMORY: the unpack warps write the dequantised weights straight from registers
 // into TMEM (tcgen05.st), so they never pass through shared memory.  (With A in shared memory every
 // M=128,N=16 MMA re-reads 4 KB of A for 16 columns of use, which by itself saturates the 128 B/clk
 // shared-memory port and starves the unpack warps that share it.)
-// One persistent CTA per SM owns a contiguous, evenly dealt range of 8-column blocks and walks it
-// in strips of <= 128 columns, full K each (no split-K, no cross-CTA reduction).
-//   warp 8, one lane : TMA box copies of the packed codes of a (strip, 256-k chunk) -- one 4 KB box per
-//                      32 columns, 128-byte swizzled -- into a ring of chunk buffers, plus the strip's scales
-//   warps 10-11      : stage x for each chunk in shared memory (k order of the unpack, canonical K-major
-//                      core-matrix layout); x is the B operand, read through a shared-memory descriptor
-//   warps 0-7        : thread = one column of the strip (TMEM lane); warp w owns lane quarter w % 4 and k half
-//                      w / 4 of every 256-k stage (= chunk): 16-byte shared loads of codes -> dequant -> tcgen05.st
-//   warps 9, 12-14   : MMA issuers, one lane each.  A warp gets a tcgen05.mma out only every ~100 cycles, whatever
-//                      the shape (measured: 94-118 cycles per M=128 MMA for N = 16 .. 128), while four warps
-//                      issuing side by side reach one per ~29 cycles.  So the 8 K=16 blocks of a stage are dealt
-//                      round-robin to 4 issuers, each accumulating into its OWN 128 x 16 FP32 accumulator, then
-//                      tcgen05.commit onto the barriers (count 4) that hand the stage / x buffer back and
-//                      announce the finished strip
-//   warps 0-3        : epilogue -- tcgen05.ld of the four accumulators, summed in fixed order, bias, FP16 store
-// TMEM columns (512 allocated; the kernel is alone on its SM): 16 i .. accumulator of issuer i, 64 + 64 s .. A stage s.
+//
+// One persistent CTA per SM owns a contiguous, evenly dealt range of 32-column units and walks it in
+// strips of <= 4 units, full K each (no cross-CTA reduction).  A warp may touch only the TMEM lane quarter
+// warp % 4, so a strip narrower than 128 columns would leave unpack warps idle.  Instead K is split S ways
+// over the lane quarters (S = 4 for a 1-unit strip, 2 for 2 units, 1 otherwise): quarter lq holds columns
+// of unit lq % (4/S) for the k range lq / (4/S), and B gets 16 S rows, rows 16 ks .. 16 ks + 15 being x over
+// k range ks.  An MMA then multiplies every lane with every k range; lane quarter lq keeps only the block of
+// 16 accumulator columns that belongs to its own range, and the S partial sums of a column meet in shared
+// memory in a fixed order.  (N = 64 costs the tensor pipe no more than N = 16 here: the MMA rate is bound by
+// issue, see below.)
+//   TMA warp, one lane : box copies of the packed codes of a (strip, 256-k step): one 4 KB, 128-byte swizzled
+//                        box per live lane quarter, into a ring of step buffers; plus the strip's scales
+//   x warps (2)        : one lane issues one TMA box per k range ([16 rows][256 k], 512-byte rows; a box whose
+//                        inner extent is one 16-byte unit would land the operand layout directly, but TMA moves
+//                        such boxes unit by unit and was slower than the whole unpack); both warps then move every
+//                        16-byte unit to its place in the canonical K-major core-matrix layout ([k group][8 rows]
+//                        [8 k]), reordering its 8 k to the order the unpack produces, and hand the buffer to the MMAs
+//   unpack warps (8)   : thread = one TMEM lane; warp w owns lane quarter w % 4 and k half w / 4 of every step:
+//                        16-byte shared loads of codes -> dequant -> tcgen05.st
+//   MMA warps (4)      : one lane each.  A warp gets a tcgen05.mma out only every ~100 cycles, whatever the shape
+//                        (measured: 94-118 cycles per M=128 MMA for N = 16 .. 128), while four warps issuing side
+//                        by side reach one per ~29 cycles.  So the 16 K=16 blocks of a step are dealt round-robin
+//                        to 4 issuers, each accumulating into its OWN accumulator, then tcgen05.commit onto the
+//                        barriers (count 4) that hand the stage / x buffer back and announce the finished strip
+//   unpack warps 0-3   : epilogue -- tcgen05.ld of the four accumulators, summed in fixed order, (S > 1: the
+//                        k-range partials through shared memory,) bias, FP16 store
+// TMEM columns (512 allocated; the kernel is alone on its SM): 64 i .. accumulator of issuer i (16 S used),
+// 256 + 128 s .. A stage s.
 // Every wait is time-bounded; on a timeout the kernel raises g_w4_fault, stops issuing work, and still
 // frees its TMEM columns before it returns.
-constexpr int kUChunkK = 256;                  // k per packed chunk
-constexpr int kUPackedBufs = 8;                // packed chunks in flight (16 KB each at 128 columns)
-constexpr int kUStageK = 256;                  // k per unpack/MMA stage (= one packed chunk: fewer hand-offs per k)
-constexpr int kUStages = 3;                    // A operand stages in TMEM
-constexpr int kUTmemCols = 512;                // allocation (power of two)
-constexpr int kUTmemA = 64;                    // first column of A stage 0
-constexpr int kUStageCols = kUStageK / 2;      // 32-bit TMEM columns per stage (two FP16 k per column)
-static_assert(kUTmemA + kUStages * kUStageCols <= kUTmemCols, "A stages must fit the TMEM allocation");
-constexpr int kUXLbo = 128, kUXSbo = (kUChunkK / 8) * kUXLbo;  // x chunk: [2 row groups][32 k groups][8 x 16 B]
-constexpr int kUXBytes = 2 * kUXSbo;
-constexpr int kUPackedBytes = 16 * 8 * (kUChunkK / 2);  // packed codes of a 128-column strip chunk
+constexpr int kUStepK = 256;                   // k per step: one packed box row (128 bytes), one A stage
+constexpr int kUPackedBufs = 4;                // packed steps in flight (16 KB each)
+constexpr int kUStages = 2;                    // A operand stages in TMEM
+constexpr int kUXBufs = 2;                     // x step buffers (raw and operand layout each)
 constexpr int kUIssuers = 4;                   // MMA-issuing warps, one accumulator each
-constexpr int kUThreads = 15 * 32;             // 8 unpack warps, TMA warp, MMA warp 0, 2 x-staging warps, MMA warps 1-3
+constexpr int kUTmemCols = 512;                // allocation (power of two)
+constexpr int kUAccCols = 64;                  // TMEM columns reserved per issuer (16 S <= 64)
+constexpr int kUTmemA = kUIssuers * kUAccCols; // first column of A stage 0
+constexpr int kUStageCols = kUStepK / 2;       // 32-bit TMEM columns per stage (two FP16 k per column)
+static_assert(kUTmemA + kUStages * kUStageCols <= kUTmemCols, "A stages must fit the TMEM allocation");
+constexpr int kUXLbo = 128, kUXSbo = (kUStepK / 8) * kUXLbo;  // x: [row group of 8][32 k groups][8 rows x 16 B]
+constexpr int kUXBytes = 8 * kUXSbo;           // up to 64 rows (S = 4)
+constexpr int kUPackedBytes = 4 * 32 * (kUStepK / 2);  // 4 lane quarters x 32 rows x 128 B
+constexpr int kURedBytes = 128 * 16 * 4;       // k-range partials: [lane][16] floats
+constexpr int kWTma = 8, kWMma0 = 9, kWX0 = 10, kWMma1 = 12;  // warp roles; 0-7 unpack, 10-11 x, 12-14 MMA
+constexpr int kUThreads = 15 * 32;
 
 struct UmmaPlan {
-  int ctas, total_blocks, chunks;  // total_blocks counts 32-column units
-  int scale_row_bytes;  // bytes of scales per column (groups * 2)
+  int ctas, total_units;  // 32-column units
 };
+
+// The K split of a strip of `units` 32-column units.
+__host__ __device__ inline int umma_split(int units, int k) {
+  if (units == 1 && k % (4 * kUStepK) == 0) return 4;
+  if (units <= 2 && k % (2 * kUStepK) == 0) return 2;
+  return 1;
+}
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, int lbo, int sbo) {
   return static_cast<uint64_t>((smem_addr >> 4) & 0x3fff) | (static_cast<uint64_t>((lbo >> 4) & 0x3fff) << 16) |
@@ -601,6 +622,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -610,37 +639,67 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Walks the CTA's strips and steps in the one order every role follows.
+struct UmmaCursor {
+  int unit, unit_end, k;  // next strip starts at `unit`
+  int units, split, steps, kper;  // current strip
+  int kc;                          // step inside the strip
+  int q;                           // steps since the kernel started
+  __device__ bool begin_strip() {
+    if (unit >= unit_end) return false;
+    units = min(4, unit_end - unit);
+    split = umma_split(units, k);
+    kper = k / split;
+    steps = kper / kUStepK;
+    kc = 0;
+    return true;
+  }
+  __device__ bool next_step() {  // false: the strip is finished, the cursor sits on the next one
+    ++q;
+    if (++kc < steps) return true;
+    unit += units;
+    return false;
+  }
+};
 
 __global__ void __launch_bounds__(kUThreads, 1)
-w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap) {
+w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+                  const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* packed = smem_raw;                                   // [kUPackedBufs][kUPackedBytes]
-  unsigned char* xbuf = packed + kUPackedBufs * kUPackedBytes;        // [2][kUXBytes]
-  unsigned char* scbuf = xbuf + 2 * kUXBytes;                         // [16 blocks][8 cols][scale_row_bytes]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(scbuf + 16 * 8 * plan.scale_row_bytes);
-  uint64_t* pk_full = bars;                       // [kUPackedBufs]  TMA bytes of a packed chunk landed
-  uint64_t* pk_empty = bars + kUPackedBufs;       // [kUPackedBufs]  the 8 unpack warps are done with the chunk
-  uint64_t* a_full = bars + 2 * kUPackedBufs;     // [kUStages] the 8 unpack warps wrote the stage to TMEM
-  uint64_t* a_empty = a_full + kUStages;          // [kUStages] MMAs that read the stage completed (commit)
-  uint64_t* x_full = a_empty + kUStages;          // [2]
-  uint64_t* x_empty = x_full + 2;                // [2]
-  uint64_t* sc_full = x_empty + 2;               // [1]
-  uint64_t* acc_full = sc_full + 1;              // [1]
+  unsigned char* packed = smem_raw;                                 // [kUPackedBufs][kUPackedBytes]
+  unsigned char* xbuf = packed + kUPackedBufs * kUPackedBytes;      // [kUXBufs][kUXBytes]
+  unsigned char* xraw = xbuf + kUXBufs * kUXBytes;                  // [kUXBufs][4 k ranges][16 rows][256 k] as TMA lands it
+  unsigned char* scbuf = xraw + kUXBufs * kUXBytes;                 // [128 lanes][scale_row_bytes]
+  const int scale_row_bytes = a.groups * 2;
+  float* red = reinterpret_cast<float*>(scbuf + 128 * scale_row_bytes);  // [128 lanes][16]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(red) + kURedBytes);
+  uint64_t* pk_full = bars;                       // [kUPackedBufs]  TMA bytes of a packed step landed
+  uint64_t* pk_empty = pk_full + kUPackedBufs;    // [kUPackedBufs]  the 8 unpack warps are done with the step
+  uint64_t* a_full = pk_empty + kUPackedBufs;     // [kUStages] the 8 unpack warps wrote the stage to TMEM
+  uint64_t* a_empty = a_full + kUStages;          // [kUStages] every issuer's MMAs that read the stage completed
+  uint64_t* x_raw = a_empty + kUStages;           // [kUXBufs] TMA bytes of an x step landed
+  uint64_t* x_full = x_raw + kUXBufs;             // [kUXBufs] both x warps reordered their share
+  uint64_t* x_empty = x_full + kUXBufs;           // [kUXBufs] every issuer's MMAs that read the buffer completed
+  uint64_t* sc_full = x_empty + kUXBufs;          // [1]
+  uint64_t* acc_full = sc_full + 1;               // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the CTA's range of 8-column blocks, dealt in units of 4 blocks (one TMEM lane quarter, one 32-row TMA box)
-  const int blk_begin = 4 * static_cast<int>(static_cast<int64_t>(blockIdx.x) * plan.total_blocks / plan.ctas);
-  const int blk_end = 4 * static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * plan.total_blocks / plan.ctas);
   const int scale_shift = 31 - __clz(a.group);
+  UmmaCursor cur;
+  cur.unit = static_cast<int>(static_cast<int64_t>(blockIdx.x) * plan.total_units / plan.ctas);
+  cur.unit_end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * plan.total_units / plan.ctas);
+  cur.k = a.k;
+  cur.q = 0;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kUPackedBufs; ++i) {
       mbar_init(pk_full + i, 1);
       mbar_init(pk_empty + i, 8);   // one arrival per unpack warp
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(x_full + i, 2);   // one arrival per x-staging warp
+    for (int i = 0; i < kUXBufs; ++i) {
+      mbar_init(x_raw + i, 1);
+      mbar_init(x_full + i, 1);     // one x thread, after the x warps met
       mbar_init(x_empty + i, kUIssuers);
     }
     for (int i = 0; i < kUStages; ++i) {
@@ -651,241 +710,262 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
     mbar_init(acc_full, kUIssuers);
     mbar_fence_init();
   }
-  if (warp == 9) {  // TMEM: accumulator + A stages
+  if (warp == kWMma0) {  // TMEM: accumulators + A stages
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(kUTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == kWTma) {
+    // ------------------------------------------------------------ TMA producer: packed codes and scales
     if (lane == 0) {
-      int q = 0, strip_i = 0;  // chunk counter over the CTA's life, strip counter
       bool ok = true;
-      for (int b0 = blk_begin; b0 < blk_end && ok; b0 += 16, ++strip_i) {
-        const int nb = min(16, blk_end - b0);
-        // scales of the strip (whole K): wait until the previous strip's readers are done = its last chunk buffer was released
+      int strip_i = 0;
+      while (ok && cur.begin_strip()) {
+        const int qpk = 4 / cur.split;  // lane quarters per k range = units the strip can hold
+        // scales of the strip (whole K, once per live lane quarter): the buffer is free once the unpack warps
+        // have released the last packed step of the previous strip
         if (strip_i > 0) {
-          const int prev = q - 1;  // last chunk of the previous strip
+          const int prev = cur.q - 1;
           ok = mbar_wait(pk_empty + prev % kUPackedBufs, (prev / kUPackedBufs) & 1);
           if (!ok) break;
         }
-        mbar_expect_tx(sc_full, static_cast<unsigned>(nb * 8 * plan.scale_row_bytes));
-        for (int b = 0; b < nb; b += 4) tma_box_2d(scbuf + b * 8 * plan.scale_row_bytes, &smap, 0, (b0 + b) * 8, sc_full);
-        for (int kc = 0; kc < plan.chunks; ++kc, ++q) {
-          const int buf = q % kUPackedBufs;
-          if (q >= kUPackedBufs && !mbar_wait(pk_empty + buf, ((q / kUPackedBufs) - 1) & 1)) {
+        mbar_expect_tx(sc_full, static_cast<unsigned>(cur.units * cur.split * 32 * scale_row_bytes));
+        for (int lq = 0; lq < 4; ++lq)
+          if (lq % qpk < cur.units) tma_box_2d(scbuf + lq * 32 * scale_row_bytes, &smap, 0, (cur.unit + lq % qpk) * 32, sc_full);
+        do {
+          const int buf = cur.q % kUPackedBufs;
+          if (cur.q >= kUPackedBufs && !mbar_wait(pk_empty + buf, ((cur.q / kUPackedBufs) - 1) & 1)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(pk_full + buf, static_cast<unsigned>(nb * 8 * (kUChunkK / 2)));
-          for (int b = 0; b < nb; b += 4)  // 32-row boxes; the 128-byte swizzle depends on (row & 7) only, so rows stay where 8-row boxes put them
-            tma_box_2d(packed + buf * kUPackedBytes + b * 8 * (kUChunkK / 2), &wmap, kc * (kUChunkK / 8), (b0 + b) * 8, pk_full + buf);
-        }
+          mbar_expect_tx(pk_full + buf, static_cast<unsigned>(cur.units * cur.split * 32 * (kUStepK / 2)));
+          for (int lq = 0; lq < 4; ++lq)  // 32-row boxes; the 128-byte swizzle depends on (row & 7) only
+            if (lq % qpk < cur.units)
+              tma_box_2d(packed + buf * kUPackedBytes + lq * 32 * (kUStepK / 2), &wmap,
+                         ((lq / qpk) * cur.kper + cur.kc * kUStepK) / 8, (cur.unit + lq % qpk) * 32, pk_full + buf);
+        } while (cur.next_step());
+        ++strip_i;
       }
       if (!ok) atomicOr(&g_w4_fault, 4u);
     }
-  } else if (warp == 9 || warp >= 12) {
+  } else if (warp == kWMma0 || warp >= kWMma1) {
     // ------------------------------------------------------------ MMA issuers
     if (lane == 0) {
-      constexpr uint32_t kIdesc = (1u << 4) | (2u << 17) | (8u << 24);  // D = F32, A = B = F16 K-major, N = 16, M = 128
-      const int issuer = warp == 9 ? 0 : warp - 11;
-      const uint32_t acc = tmem_acc + issuer * 16;
+      const int issuer = warp == kWMma0 ? 0 : warp - kWMma1 + 1;
+      const uint32_t acc = tmem_base + issuer * kUAccCols;
       // x descriptor: only the 14-bit start-address field changes from MMA to MMA
       const uint64_t xd0 = umma_desc(smem_u32(xbuf), kUXLbo, kUXSbo);
       const uint32_t xd_lo = static_cast<uint32_t>(xd0), xd_hi = static_cast<uint32_t>(xd0 >> 32);
-      int q = 0, sq = 0;  // chunk counter, stage counter
       bool ok = true;
-      for (int b0 = blk_begin; b0 < blk_end && ok; b0 += 16) {
-        for (int kc = 0; kc < plan.chunks && ok; ++kc, ++q) {
-          const int xb = q & 1;
-          ok = mbar_wait(x_full + xb, (q >> 1) & 1);
-          for (int st = 0; st < kUChunkK / kUStageK && ok; ++st, ++sq) {
-            const int s = sq % kUStages;
-            ok = mbar_wait(a_full + s, (sq / kUStages) & 1);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t a_base = tmem_acc + kUTmemA + s * kUStageCols + issuer * 8;
-            const uint32_t x_lo = xd_lo + ((xb * kUXBytes + (st * (kUStageK / 8) + issuer * 2) * kUXLbo) >> 4);
+      while (ok && cur.begin_strip()) {
+        // D = F32, A = B = F16 K-major, N = 16 S, M = 128
+        const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(2 * cur.split) << 17) | (8u << 24);
+        do {
+          const int xb = cur.q % kUXBufs, s = cur.q % kUStages;
+          ok = mbar_wait(x_full + xb, (cur.q / kUXBufs) & 1) && mbar_wait(a_full + s, (cur.q / kUStages) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_base = tmem_base + kUTmemA + s * kUStageCols + issuer * 8;
+          const uint32_t x_lo = xd_lo + ((xb * kUXBytes + issuer * 2 * kUXLbo) >> 4);
 #pragma unroll
-            for (int j = 0; j < kUStageK / 16 / kUIssuers; ++j) {  // K blocks issuer, issuer + 4, ...
-              uint64_t xd;
-              asm("mov.b64 %0, {%1, %2};" : "=l"(xd) : "r"(x_lo + ((j * kUIssuers * 2 * kUXLbo) >> 4)), "r"(xd_hi));
-              umma_f16_ta(acc, a_base + j * kUIssuers * 8, xd, kIdesc, !(kc == 0 && st == 0 && j == 0));
-            }
-            umma_commit(a_empty + s);  // the TMEM stage is free once every issuer's MMAs have read it
+          for (int j = 0; j < kUStepK / 16 / kUIssuers; ++j) {  // K blocks issuer, issuer + 4, ...
+            uint64_t xd;
+            asm("mov.b64 %0, {%1, %2};" : "=l"(xd) : "r"(x_lo + ((j * kUIssuers * 2 * kUXLbo) >> 4)), "r"(xd_hi));
+            umma_f16_ta(acc, a_base + j * kUIssuers * 8, xd, idesc, !(cur.kc == 0 && j == 0));
           }
-          if (ok) umma_commit(x_empty + xb);
-        }
+          umma_commit(a_empty + s);   // the TMEM stage is free once every issuer's MMAs have read it
+          umma_commit(x_empty + xb);
+        } while (cur.next_step());
         if (ok) umma_commit(acc_full);
       }
       if (!ok) atomicOr(&g_w4_fault, 8u);
     }
-  } else if (warp >= 10) {  // 10, 11
-    // ------------------------------------------------------------ x staging warps
-    // x chunk -> canonical K-major layout with the unpack's k order inside each 8-block.  The global loads
-    // of a chunk are issued one chunk ahead, so only the permute + stores sit between two hand-offs.
-    const int t = threadIdx.x - 320;  // 0 .. 63
-    U4 xin[8];
-    auto load_x = [&](int kc) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int idx = t + i * 64;  // 16 rows x 32 k groups; a warp covers 8 rows x 4 k groups = 512 contiguous bytes of xbuf
-        const int m = (idx & 7) | ((idx >> 8) << 3), kg = (idx >> 3) & 31;
-        xin[i] = U4{0u, 0u, 0u, 0u};
-        if (m < a.m) xin[i] = ld_cached16(a.x + static_cast<size_t>(m) * a.k + kc * kUChunkK + kg * 8);
-      }
-    };
-    load_x(0);
-    int q = 0;
+  } else if (warp >= kWX0) {
+    // ------------------------------------------------------------ x warps
+    const int t = threadIdx.x - kWX0 * 32;  // 0 .. 63
     bool ok = true;
-    for (int b0 = blk_begin; b0 < blk_end; b0 += 16) {
-      for (int kc = 0; kc < plan.chunks; ++kc, ++q) {
-        const int xb = q & 1;
-        if (ok && q >= 2) ok = mbar_wait(x_empty + xb, ((q >> 1) - 1) & 1);
+    UmmaCursor ahead = cur;  // issues the loads, kUXBufs steps in front of `cur`
+    bool ahead_live = ahead.begin_strip();
+    auto issue = [&]() {  // raw buffer ahead.q % kUXBufs is free: its last readers passed the x-warp barrier
+      if (!ahead_live) return;
+      if (t == 0) {
+        const int xb = ahead.q % kUXBufs;
+        mbar_expect_tx(x_raw + xb, static_cast<unsigned>(ahead.split * 16 * kUStepK * 2));
+        for (int ks = 0; ks < ahead.split; ++ks)  // rows >= M are out of range: zero-filled, still counted
+          tma_box_2d(xraw + xb * kUXBytes + ks * 16 * kUStepK * 2, &xmap, ks * ahead.kper + ahead.kc * kUStepK, 0, x_raw + xb);
+      }
+      if (!ahead.next_step()) ahead_live = ahead.begin_strip();
+    };
+    for (int i = 0; i < kUXBufs; ++i) issue();
+    // A quarter warp moves an 8-row x 8-k-group block per pass along its diagonals: lane i takes k group i of row
+    // (i + r) & 7, so the eight 16-byte loads (row pitch 512 B) and the eight stores (k-group pitch 128 B) each hit
+    // eight different bank groups.
+    const int qw = t >> 3, li = t & 7;        // 8 quarter warps: (row group, quarter of the 32 k groups)
+    const int mg = qw >> 2, kg = (qw & 3) * 8 + li;
+    while (cur.begin_strip()) {
+      do {
+        const int xb = cur.q % kUXBufs;
+        if (ok) ok = mbar_wait(x_raw + xb, (cur.q / kUXBufs) & 1);
+        if (ok && cur.q >= kUXBufs) ok = mbar_wait(x_empty + xb, ((cur.q / kUXBufs) - 1) & 1);
         if (ok) {
+          for (int ks = 0; ks < cur.split; ++ks) {
+            const unsigned char* src = xraw + xb * kUXBytes + ks * 16 * kUStepK * 2 + kg * 16;
+            unsigned char* dst = xbuf + xb * kUXBytes + (ks * 2 + mg) * kUXSbo + kg * kUXLbo;
+            U4 v[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int idx = t + i * 64;
-            const int m = (idx & 7) | ((idx >> 8) << 3), kg = (idx >> 3) & 31;
-            U4 v;
-            v.x = __byte_perm(xin[i].x, xin[i].z, 0x5410);
-            v.y = __byte_perm(xin[i].x, xin[i].z, 0x7632);
-            v.z = __byte_perm(xin[i].y, xin[i].w, 0x5410);
-            v.w = __byte_perm(xin[i].y, xin[i].w, 0x7632);
-            *reinterpret_cast<U4*>(xbuf + xb * kUXBytes + (m >> 3) * kUXSbo + kg * kUXLbo + (m & 7) * 16) = v;
+            for (int r = 0; r < 8; ++r) v[r] = *reinterpret_cast<const U4*>(src + (mg * 8 + ((li + r) & 7)) * (kUStepK * 2));
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              U4 o;  // k 0..7 of one row -> 0,4,1,5,2,6,3,7, the order the unpack produces
+              o.x = __byte_perm(v[r].x, v[r].z, 0x5410);
+              o.y = __byte_perm(v[r].x, v[r].z, 0x7632);
+              o.z = __byte_perm(v[r].y, v[r].w, 0x5410);
+              o.w = __byte_perm(v[r].y, v[r].w, 0x7632);
+              *reinterpret_cast<U4*>(dst + ((li + r) & 7) * 16) = o;
+            }
           }
           fence_async_smem();
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cta(x_full + xb);
-        load_x(kc + 1 < plan.chunks ? kc + 1 : 0);  // next chunk (x does not depend on the strip)
-      }
+        asm volatile("bar.sync 2, 64;" ::: "memory");  // both x warps are done with the raw buffer and wrote their share
+        if (t == 0) mbar_arrive_cta(x_full + xb);
+        issue();
+      } while (cur.next_step());
     }
     if (!ok && lane == 0) atomicOr(&g_w4_fault, 32u);
   } else {
     // ------------------------------------------------------------ unpack warps (+ epilogue)
-    const int lq = warp & 3, kh = warp >> 2;  // TMEM lane quarter this warp may touch, k half of a stage
-    const int c = lq * 32 + lane;             // this thread's column of the strip = its TMEM lane
-    const uint32_t a_lane_base = tmem_acc + (static_cast<uint32_t>(lq * 32) << 16) + kUTmemA + kh * (kUStageCols / 2);
-    int q = 0, sq = 0, strip_i = 0;
+    const int lq = warp & 3, kh = warp >> 2;  // TMEM lane quarter this warp may touch, k half of a step
+    const int c = lq * 32 + lane;             // this thread's TMEM lane
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(lq * 32) << 16);
+    const uint32_t a_lane_base = lane_base + kUTmemA + kh * (kUStageCols / 2);
+    const __half* sc_row = reinterpret_cast<const __half*>(scbuf + c * scale_row_bytes);
+    int strip_i = 0;
     bool ok = true;
-    for (int b0 = blk_begin; b0 < blk_end; b0 += 16, ++strip_i) {
-      const int nb = min(16, blk_end - b0);
-      const int ncols = nb * 8;
-      const bool warp_live = lq * 32 < ncols;  // warp-uniform: a quarter without columns writes nothing
+    while (cur.begin_strip()) {
+      const int qpk = 4 / cur.split;
+      const int ks = lq / qpk, uq = lq % qpk;   // this quarter's k range and unit of the strip
+      const bool warp_live = uq < cur.units;    // warp-uniform: a quarter without columns writes nothing
+      const int col = (cur.unit + uq) * 32 + lane;  // output column of this thread
+      const int k_range0 = ks * cur.kper;
+      const int split = cur.split;
       if (ok) ok = mbar_wait(sc_full, strip_i & 1);
-      const unsigned char* sc_row = scbuf + c * plan.scale_row_bytes;
-      for (int kc = 0; kc < plan.chunks; ++kc, ++q) {
-        const int buf = q % kUPackedBufs;
-        if (ok) ok = mbar_wait(pk_full + buf, (q / kUPackedBufs) & 1);
-        // packed tiles arrive 128-byte swizzled: 16-byte piece p of row r sits at piece p ^ (r & 7), so the
-        // lanes of a warp, which read the same piece of 32 different rows, spread over all bank groups
-        const unsigned char* row = packed + buf * kUPackedBytes + (c >> 3) * 8 * (kUChunkK / 2) + (c & 7) * (kUChunkK / 2);
-        for (int st = 0; st < kUChunkK / kUStageK; ++st, ++sq) {
-          const int s = sq % kUStages;
-          if (ok && sq >= kUStages) ok = mbar_wait(a_empty + s, ((sq / kUStages) - 1) & 1);
-          if (ok && warp_live) {
-            tc_fence_after();
-            const int k_half = kc * kUChunkK + st * kUStageK + kh * (kUStageK / 2);
+      do {
+        const int buf = cur.q % kUPackedBufs, s = cur.q % kUStages;
+        if (ok) ok = mbar_wait(pk_full + buf, (cur.q / kUPackedBufs) & 1);
+        if (ok && cur.q >= kUStages) ok = mbar_wait(a_empty + s, ((cur.q / kUStages) - 1) & 1);
+        if (ok && warp_live) {
+          tc_fence_after();
+          // packed tiles arrive 128-byte swizzled: 16-byte piece p of row r sits at piece p ^ (r & 7), so the
+          // lanes of a warp, which read the same piece of 32 different rows, spread over all bank groups
+          const unsigned char* row = packed + buf * kUPackedBytes + c * (kUStepK / 2);
+          const int k_half = k_range0 + cur.kc * kUStepK + kh * (kUStepK / 2);
 #pragma unroll
-            for (int pc = 0; pc < kUStageK / 64; ++pc) {
-              // two pieces = 64 k lie inside one group (group >= 64)
-              const __half2 s2 = __half2half2(reinterpret_cast<const __half*>(sc_row)[(k_half + (pc & ~1) * 32) >> scale_shift]);
-              const int piece = st * (kUStageK / 32) + kh * (kUStageK / 64) + pc;
-              U4 wv = U4{0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};  // code 8 = weight 0 for columns past the strip
-              if (c < ncols) wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));
-              uint32_t r[16];
+          for (int pc = 0; pc < kUStepK / 64; ++pc) {
+            // two pieces = 64 k lie inside one group (group >= 64)
+            const __half2 s2 = __half2half2(sc_row[(k_half + (pc & ~1) * 32) >> scale_shift]);
+            const int piece = kh * (kUStepK / 64) + pc;
+            const U4 wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));  // rows past N are zero-filled: harmless
+            uint32_t r[16];
 #pragma unroll
-              for (int w = 0; w < 4; ++w) {
-                const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
-                __half2 h[4];
-                dequant8(word, s2, h);
+            for (int w = 0; w < 4; ++w) {
+              const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
+              __half2 h[4];
+              dequant8(word, s2, h);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) r[4 * w + i] = *reinterpret_cast<uint32_t*>(&h[i]);
-              }
-              tmem_st16(a_lane_base + s * kUStageCols + pc * 16, r);
+              for (int i = 0; i < 4; ++i) r[4 * w + i] = *reinterpret_cast<uint32_t*>(&h[i]);
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            tc_fence_before();
+            tmem_st16(a_lane_base + s * kUStageCols + pc * 16, r);
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cta(a_full + s);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tc_fence_before();
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive_cta(pk_empty + buf);
-      }
-      // ---- epilogue of the strip: warps 0-3 read TMEM lanes 32*warp .. +31 = columns of the strip
+        if (lane == 0) {
+          mbar_arrive_cta(a_full + s);
+          mbar_arrive_cta(pk_empty + buf);
+        }
+      } while (cur.next_step());
+      // ---- epilogue of the strip: warps 0-3 read their own lane quarter of the four accumulators
+      float sum[16];
       if (warp < 4) {
         if (ok) ok = mbar_wait(acc_full, strip_i & 1);
-        if (ok) {
+        if (ok && warp_live) {
           tc_fence_after();
-          float sum[16];
-          const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
 #pragma unroll
           for (int i = 0; i < kUIssuers; ++i) {
             uint32_t r[16];
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                : "r"(taddr + i * 16));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tmem_ld16(lane_base + i * kUAccCols + ks * 16, r);  // the 16 accumulator columns of this quarter's own k range
 #pragma unroll
             for (int m = 0; m < 16; ++m) sum[m] = i == 0 ? __uint_as_float(r[m]) : __fadd_rn(sum[m], __uint_as_float(r[m]));
           }
-          const int col = b0 * 8 + c;  // warps 0-3: lq == warp, so c is this thread's accumulator lane too
-          if (c < ncols && col < a.n) {
-            const float bv = a.bias ? __half2float(a.bias[col]) : 0.0f;
-#pragma unroll
-            for (int m = 0; m < 16; ++m)
-              if (m < a.m) a.y[static_cast<size_t>(m) * a.n + col] = __float2half_rn(sum[m] + bv);
-          }
           tc_fence_before();
+          if (split > 1) {
+#pragma unroll
+            for (int m = 0; m < 16; m += 4)
+              *reinterpret_cast<float4*>(red + c * 16 + m) = make_float4(sum[m], sum[m + 1], sum[m + 2], sum[m + 3]);
+          }
         }
       }
-      // all 256 threads meet before the next strip's stages can reach the MMA warp (its a_full needs all of them),
-      // so the next strip's first MMA cannot overwrite TMEM while it is still being read
+      if (split > 1) {
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // strip-uniform: the k-range partials are in shared memory
+        if (warp < 4 && ok && warp_live && ks == 0) {
+          for (int j = 1; j < split; ++j)  // fixed order: k range 0 + 1 + 2 + 3
+#pragma unroll
+            for (int m = 0; m < 16; ++m) sum[m] = __fadd_rn(sum[m], red[(c + j * qpk * 32) * 16 + m]);
+        }
+      }
+      if (warp < 4 && ok && warp_live && ks == 0 && col < a.n) {
+        const float bv = a.bias ? __half2float(a.bias[col]) : 0.0f;
+#pragma unroll
+        for (int m = 0; m < 16; ++m)
+          if (m < a.m) a.y[static_cast<size_t>(m) * a.n + col] = __float2half_rn(sum[m] + bv);
+      }
+      // all 256 threads meet before the next strip's stages can reach the MMA warps (a_full needs all of them),
+      // so the next strip's first MMAs cannot overwrite TMEM (nor its partials the shared buffer) while they are read
       asm volatile("bar.sync 1, 256;" ::: "memory");
+      ++strip_i;
     }
     if (!ok && lane == 0) atomicOr(&g_w4_fault, 16u);
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kWMma0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "n"(kUTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kUTmemCols) : "memory");
   }
 }
 
 int launch_umma(const W4Args& a, cudaStream_t stream) {
   UmmaPlan plan;
-  plan.total_blocks = (a.n + 31) / 32;  // units of 32 columns
-  plan.ctas = plan.total_blocks < sm_count() ? plan.total_blocks : sm_count();
-  plan.chunks = a.k / kUChunkK;
-  plan.scale_row_bytes = a.groups * 2;
-  const size_t smem = kUPackedBufs * kUPackedBytes + 2 * kUXBytes + 16 * 8 * plan.scale_row_bytes + 48 * sizeof(uint64_t);
-  if (smem > 220 * 1024) return XDK_ERR_LIMIT;
-  CUtensorMap wmap, smap;
+  plan.total_units = (a.n + 31) / 32;
+  plan.ctas = plan.total_units < sm_count() ? plan.total_units : sm_count();
+  const size_t smem = kUPackedBufs * kUPackedBytes + 2 * kUXBufs * kUXBytes + 128 * a.groups * 2 + kURedBytes + 48 * sizeof(uint64_t);
+  if (smem > 225 * 1024) return XDK_ERR_LIMIT;
+  CUtensorMap wmap, smap, xmap;
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k / 8), static_cast<cuuint64_t>(a.n)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k / 2)};
-    const cuuint32_t box[2] = {kUChunkK / 8, 32};
+    const cuuint32_t box[2] = {kUStepK / 8, 32};
     const cuuint64_t sdims[2] = {static_cast<cuuint64_t>(a.groups), static_cast<cuuint64_t>(a.n)};
     const cuuint64_t sstrides[1] = {static_cast<cuuint64_t>(a.groups) * 2};
     const cuuint32_t sbox[2] = {static_cast<cuuint32_t>(a.groups), 32};
-    static_assert(kUChunkK / 2 == 128, "the packed box is one 128-byte swizzle span wide");
-    if (!encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.packed, dims, strides, box, true) ||
-        !encode_tiled_2d(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, sdims, sstrides, sbox, false))
+    static_assert(kUStepK / 2 == 128, "the packed box is one 128-byte swizzle span wide");
+    if (!encode_tiled(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a.packed, dims, strides, box, true) ||
+        !encode_tiled(&smap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.scales, sdims, sstrides, sbox, false))
       return XDK_ERR_LAUNCH;
+    const cuuint64_t xdims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
+    const cuuint64_t xstrides[1] = {static_cast<cuuint64_t>(a.k) * 2};
+    const cuuint32_t xbox[2] = {kUStepK, 16};
+    if (!encode_tiled(&xmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.x, xdims, xstrides, xbox, false)) return XDK_ERR_LAUNCH;
   }
   cudaError_t err = cudaFuncSetAttribute(w4a16_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return note_launch(err);
-  return launch(w4a16_umma_kernel, dim3(plan.ctas), dim3(kUThreads), smem, stream, 1u, a, plan, wmap, smap);
+  return launch(w4a16_umma_kernel, dim3(plan.ctas), dim3(kUThreads), smem, stream, 1u, a, plan, wmap, smap, xmap);
 }
 
 // Any K (odd included), any alignment: warp per column, lane per byte (two codes), rows one at a
@@ -966,13 +1046,12 @@ extern "C" int xdk_w4a16(const void* x, const uint8_t* packed, const void* scale
   a.col_groups = a.groups_per_cta = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool fast = k % 32 == 0 && aligned16(packed) && aligned16(x) && m * k * 2 <= 200 * 1024;
-  // tcgen05 kernel: taken where every SM gets at least two 32-column units (measured at K = 4096, M = 16:
-  // 18.6 vs 26.0 us at N = 14336, 32.8 vs 42.4 us at N = 28672, but 16.1 vs 12.5 us at N = 4096, where only one
-  // TMEM lane quarter per SM has columns to unpack).  XDK_W4A16_UMMA=1 / =0 forces it on (where eligible) / off.
+  // M > 8 goes to the tcgen05 kernel (measured at K = 4096, M = 16 against the mma.sync kernel: 10.0 vs 12.5 us at
+  // N = 4096, 12.8 vs 15.9 at 6144, 17.5 vs 26.0 at 14336, 31.1 vs 42.4 at 28672).  XDK_W4A16_UMMA=0 sends it to the
+  // mma.sync kernel instead (kept for comparison runs and as the path for shapes the tcgen05 kernel does not take).
   static const int umma_env = getenv("XDK_W4A16_UMMA") ? (getenv("XDK_W4A16_UMMA")[0] == '1' ? 1 : 0) : -1;
   const bool umma_ok = fast && m > 8 && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales);
-  const bool use_umma = umma_env >= 0 ? umma_env == 1 : n >= 64LL * sm_count();
-  if (use_umma && umma_ok) {
+  if (umma_env != 0 && umma_ok) {
     const int st = launch_umma(a, s);
     if (st != XDK_ERR_LIMIT) return st;
   }
