@@ -198,8 +198,8 @@ def main() -> None:
     peaks = measured_peaks()
     xs_host, xs, weights = build_gpu_sweep(rank, world)
     mark("sweep weights on device")
-    # own kernels per step: one per projection, two (stream + finish) where the tile-stream path is taken
-    launches_per_step = sum(2 if (4 < m <= 16 and K * (n // world) >= (48 << 20)) else 1 for m, n, _ in SWEEP)
+    # own kernels per step: one per projection (cluster kernels for M <= 4, the tcgen05 kernel for M = 16)
+    launches_per_step = len(SWEEP)
 
     gathered = {}
     if world > 1:

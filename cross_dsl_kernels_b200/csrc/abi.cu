@@ -87,7 +87,9 @@ int xdk_abi_version(void) { return XDK_ABI_VERSION; }
 
 int xdk_last_cuda_error(void) { return xdk::g_last_cuda_error; }
 
-unsigned xdk_fault_flags(void) { return xdk::gemv_fault_word() | (xdk::w4a16_fault_word() << 8); }
+unsigned xdk_fault_flags(void) {
+  return xdk::gemv_fault_word() | (xdk::w4a16_fault_word() << 8) | (xdk::gemv_tc_fault_word() << 16);
+}
 
 int xdk_device_supported(int device) {
   int count = 0;

@@ -29,7 +29,12 @@ bool encode_tiled_2d(CUtensorMap* map, CUtensorMapDataType type, const void* bas
 int sm_count();  // SMs of the current device (cached per device)
 // Fault words of the kernels with bounded waits (current device; synchronises).  0 = no wait ever gave up.
 unsigned gemv_fault_word();
+unsigned gemv_tc_fault_word();
 unsigned w4a16_fault_word();
+
+// tcgen05 FP32 projection (gemv_tc.cu): whether it takes the shape, and its launch
+bool gemv_tc_eligible(const float* x, const float* w, int64_t m, int64_t k, int64_t n, bool nk);
+int launch_gemv_tc(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, bool nk, cudaStream_t stream);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

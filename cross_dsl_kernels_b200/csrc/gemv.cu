@@ -704,6 +704,12 @@ extern "C" int xdk_gemv_f32(const float* x, const float* w, const float* bias, f
   if (int st = require_sm100()) return st;
   const bool nk = weight_is_nk != 0;
 
+  // 4 < M <= 16 without scratch: the tcgen05 kernel (split-TF32 products, FP32 accumulation; see gemv_tc.cu).
+  // A caller that passes scratch asks for strict FP32 FMA arithmetic and gets the tile-stream kernel below.
+  if (split_k == 0 && !scratch && gemv_tc_eligible(x, w, m, k, n, nk))
+    return launch_gemv_tc(x, w, bias, y, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
+                          static_cast<cudaStream_t>(stream));
+
   // 4 < M <= 16, a large weight matrix (the two extra launch/finish microseconds pay off from about
   // 48M elements), a scratch buffer and TMA-addressable operands: balanced persistent tile stream.
   if (split_k == 0 && m > 4 && m <= 16 && k * n >= (48LL << 20) && scratch && scratch_bytes >= xdk_gemv_scratch_bytes(m, k, n, weight_is_nk) &&

@@ -22,6 +22,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "umma.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -211,15 +212,6 @@ struct StreamPlan {
   int chunks;          // ceil(K / 1024)
   int ring_scales;     // 1: the chunk's scales travel through the ring with the weights
 };
-
-// One TMA op: the 2-D box at element coordinates (c0, c1) of `map` -> dense rows at dst; completes on `bar`.
-__device__ __forceinline__ void tma_box_2d(void* dst_smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-          smem_u32(dst_smem)),
-      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-      : "memory");
-}
 
 template <int MR>
 __global__ void __launch_bounds__(kStreamThreads, 1)
@@ -595,73 +587,6 @@ struct UmmaPlan {
   int ctas, total_units;  // 32-column units
 };
 
-// The K split of a strip of `units` 32-column units.
-__host__ __device__ inline int umma_split(int units, int k) {
-  if (units == 1 && k % (4 * kUStepK) == 0) return 4;
-  if (units <= 2 && k % (2 * kUStepK) == 0) return 2;
-  return 1;
-}
-
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, int lbo, int sbo) {
-  return static_cast<uint64_t>((smem_addr >> 4) & 0x3fff) | (static_cast<uint64_t>((lbo >> 4) & 0x3fff) << 16) |
-         (static_cast<uint64_t>((sbo >> 4) & 0x3fff) << 32) | (1ull << 46);  // version 1, no swizzle
-}
-// D (TMEM) (+)= A (TMEM) * B (shared memory descriptor)
-__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Walks the CTA's strips and steps in the one order every role follows.
-struct UmmaCursor {
-  int unit, unit_end, k;  // next strip starts at `unit`
-  int units, split, steps, kper;  // current strip
-  int kc;                          // step inside the strip
-  int q;                           // steps since the kernel started
-  __device__ bool begin_strip() {
-    if (unit >= unit_end) return false;
-    units = min(4, unit_end - unit);
-    split = umma_split(units, k);
-    kper = k / split;
-    steps = kper / kUStepK;
-    kc = 0;
-    return true;
-  }
-  __device__ bool next_step() {  // false: the strip is finished, the cursor sits on the next one
-    ++q;
-    if (++kc < steps) return true;
-    unit += units;
-    return false;
-  }
-};
-
 __global__ void __launch_bounds__(kUThreads, 1)
 w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                   const __grid_constant__ CUtensorMap xmap) {
@@ -687,10 +612,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int scale_shift = 31 - __clz(a.group);
   UmmaCursor cur;
-  cur.unit = static_cast<int>(static_cast<int64_t>(blockIdx.x) * plan.total_units / plan.ctas);
-  cur.unit_end = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * plan.total_units / plan.ctas);
-  cur.k = a.k;
-  cur.q = 0;
+  cur.init(blockIdx.x, plan.ctas, plan.total_units, a.k, kUStepK);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kUPackedBufs; ++i) {
@@ -711,8 +633,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
     mbar_fence_init();
   }
   if (warp == kWMma0) {  // TMEM: accumulators + A stages
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(kUTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc<kUTmemCols>(tmem_slot);
   }
   tc_fence_before();
   __syncthreads();
@@ -763,7 +684,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       bool ok = true;
       while (ok && cur.begin_strip()) {
         // D = F32, A = B = F16 K-major, N = 16 S, M = 128
-        const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(2 * cur.split) << 17) | (8u << 24);
+        const uint32_t idesc = umma_idesc(16 * cur.split, 0u);
         do {
           const int xb = cur.q % kUXBufs, s = cur.q % kUStages;
           ok = mbar_wait(x_full + xb, (cur.q / kUXBufs) & 1) && mbar_wait(a_full + s, (cur.q / kUStages) & 1);
@@ -880,7 +801,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
             }
             tmem_st16(a_lane_base + s * kUStageCols + pc * 16, r);
           }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tmem_wait_st();
           tc_fence_before();
         }
         __syncwarp();
@@ -936,7 +857,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
   __syncthreads();
   if (warp == kWMma0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kUTmemCols) : "memory");
+    tmem_dealloc<kUTmemCols>(tmem_base);
   }
 }
 

@@ -64,8 +64,14 @@ def fused_residual_rmsnorm(x, residual, weight, eps, *, return_residual: bool = 
     return y, (residual_out if return_residual else None)
 
 
-def decode_linear(x, weight, bias=None, *, out_dtype=None, weight_layout: str = "KN", split_k: int = 0):
-    """y = x @ W (+ bias) in FP32.  ``split_k`` in {0 (auto), 1, 2, 4, 8}."""
+def decode_linear(x, weight, bias=None, *, out_dtype=None, weight_layout: str = "KN", split_k: int = 0,
+                  strict_fp32: bool = False):
+    """y = x @ W (+ bias) in FP32.  ``split_k`` in {0 (auto), 1, 2, 4, 8}.
+
+    With ``split_k=0`` and 4 < M <= 16 a large projection runs on the tensor cores as split-TF32
+    products with FP32 accumulation (relative L2 error ~1e-6 against an FP64 product, inside the
+    projection's 1e-5 gate).  ``strict_fp32=True`` keeps such shapes on the CUDA-core tile-stream
+    kernel, whose every product and sum is an FP32 FMA; it needs a scratch block per call."""
     _need(x.dim() == 2, "x must be a 2D tensor shaped [M, K]")
     _need(weight.dim() == 2, "weight must be a 2D tensor")
     _need(weight_layout in ("KN", "NK"), "weight_layout must be 'KN' or 'NK'")
@@ -90,10 +96,10 @@ def decode_linear(x, weight, bias=None, *, out_dtype=None, weight_layout: str = 
     with torch.cuda.device(x.device):
         y = torch.empty((m, n), device=x.device, dtype=torch.float32)
         lib = _native.lib()
-        # Scratch for the balanced tile-stream path (4 < M <= 16, split_k = 0).  A fresh block from
+        # Scratch selects the balanced tile-stream path (4 < M <= 16, split_k = 0).  A fresh block from
         # torch's caching allocator per call: stream-ordered, so overlapping calls never share it,
         # and under graph capture it lives in the graph's private pool.
-        need = lib.xdk_gemv_scratch_bytes(m, k, n, int(nk)) if split_k == 0 else 0
+        need = lib.xdk_gemv_scratch_bytes(m, k, n, int(nk)) if (split_k == 0 and strict_fp32) else 0
         scratch = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
         status = lib.xdk_gemv_f32(x.data_ptr(), weight.data_ptr(), bias_ptr, y.data_ptr(), m, k, n, int(nk), split_k,
                                   scratch.data_ptr() if need else None, need, _native.stream_ptr(x.device))

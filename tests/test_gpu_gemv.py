@@ -89,27 +89,57 @@ def test_unaligned_views(layout):
 @pytest.mark.parametrize("layout", ["KN", "NK"])
 @pytest.mark.parametrize("m,k,n", [(16, 4096, 14336), (8, 4096, 14336), (5, 4100, 12300), (9, 2052, 24580), (16, 8192, 6148)])
 def test_tile_stream_path(layout, m, k, n):
-    """4 < M <= 16 on large matrices takes the persistent tile-stream kernel (scratch + finish kernel);
-    sizes off the 32 x 128 tile grid exercise the zero-filled edges."""
+    """strict_fp32: 4 < M <= 16 on large matrices takes the persistent CUDA-core tile-stream kernel
+    (scratch + finish kernel); sizes off the 32 x 128 tile grid exercise the zero-filled edges."""
     from cross_dsl_kernels_b200.ops import decode_linear
     x, w, b, w_kn = make(m, k, n, layout, True, seed=n)
+    xd, wd, bd = x.cuda(), w.cuda(), b.cuda()
+    y = decode_linear(xd, wd, bd, weight_layout=layout, strict_fp32=True)
+    gate(y, x, w_kn, b, k)
+    assert torch.equal(y, decode_linear(xd, wd, bd, weight_layout=layout, strict_fp32=True)), "deterministic"
+    gate(decode_linear(xd, wd, None, weight_layout=layout, strict_fp32=True), x, w_kn, None, k)
+
+
+@pytest.mark.parametrize("layout", ["KN", "NK"])
+@pytest.mark.parametrize("m,k,n", [
+    (16, 4096, 14336),   # 3-4 units of 32 columns per SM: no K split
+    (8, 4096, 14336),
+    (16, 4096, 4096),    # one unit per SM: K split 4 ways over the TMEM lane quarters
+    (13, 4096, 6144),    # one or two units per SM: K split 2 ways
+    (5, 4160, 12300),    # ragged last unit, K a multiple of 64 but not of 256
+    (9, 2048, 24580),    # more than four units per SM: several strips
+    (16, 8192, 6148),
+    (16, 1024, 4096),    # the smallest matrix the path takes
+    (16, 4096, 28672),
+])
+def test_tensor_core_path(layout, m, k, n):
+    """The default for 4 < M <= 16 and K % 64 == 0: tcgen05 kind::tf32 MMAs on operands split into two
+    TF32 halves (hi.hi + hi.lo + lo.hi), FP32 accumulation.  Same gate as every other projection kernel:
+    max abs error <= 2e-4 * max(1, sqrt(K / 1024)) and relative L2 error <= 1e-5 against the FP64 product."""
+    from cross_dsl_kernels_b200.ops import decode_linear
+    x, w, b, w_kn = make(m, k, n, layout, True, seed=n + m)
     xd, wd, bd = x.cuda(), w.cuda(), b.cuda()
     y = decode_linear(xd, wd, bd, weight_layout=layout)
     gate(y, x, w_kn, b, k)
     assert torch.equal(y, decode_linear(xd, wd, bd, weight_layout=layout)), "deterministic"
     gate(decode_linear(xd, wd, None, weight_layout=layout), x, w_kn, None, k)
+    # rows of x past M never reach the output: the same rows inside a taller batch give the same values
+    if m < 16:
+        tall = torch.cat([x, torch.randn(16 - m, k)]).cuda()
+        assert torch.equal(decode_linear(tall, wd, bd, weight_layout=layout)[:m], y)
 
 
-def test_linearity_at_full_size():
+@pytest.mark.parametrize("strict,bound", [(True, 2e-6), (False, 1e-5)])
+def test_linearity_at_full_size(strict, bound):
     """y(a*x1 + x2) == a*y(x1) + y(x2) up to rounding: a size-independent property."""
     from cross_dsl_kernels_b200.ops import decode_linear
     g = torch.Generator().manual_seed(4)
     k, n = 4096, 14336
     w = (torch.randn(k, n, generator=g) / 64).cuda()
     x1, x2 = torch.randn(16, k, generator=g).cuda(), torch.randn(16, k, generator=g).cuda()
-    lhs = decode_linear(2.0 * x1 + x2, w)
-    rhs = 2.0 * decode_linear(x1, w) + decode_linear(x2, w)
-    assert rel_l2(lhs.cpu(), rhs.cpu()) <= 2e-6
+    lhs = decode_linear(2.0 * x1 + x2, w, strict_fp32=strict)
+    rhs = 2.0 * decode_linear(x1, w, strict_fp32=strict) + decode_linear(x2, w, strict_fp32=strict)
+    assert rel_l2(lhs.cpu(), rhs.cpu()) <= bound
 
 
 def test_graph_replay_follows_changed_inputs_on_side_stream():
