@@ -19,16 +19,18 @@
 // lane quarters and add the S partial sums through shared memory in a fixed order; S is one value per launch
 // (4 when no CTA has more than one unit, 2 for two, else 1), which also sizes the x buffers, and whatever shared
 // memory they leave goes to the W ring.
-//   TMA warp, one lane : W tiles of a 64-k step, one box per live lane quarter (KN: [64 k][32 columns]; NK: two
-//                        128-byte swizzled [32 columns][32 k] boxes), into a ring of step buffers
+//   TMA warps (4)      : one lane each, one warp per TMEM lane quarter: the W tile of a 64-k step (NK: two 128-byte
+//                        swizzled [32 columns][32 k] boxes per quarter; KN: one [64 k][32 u columns] box per k range,
+//                        u = units of the strip, so that HBM sees runs of up to 512 bytes) into a ring of step buffers.  Four warps because a warp gets a TMA box copy out only every ~230
+//                        cycles: one producer issuing all boxes of a step was the bottleneck (NK slower than KN)
 //   x warps (2)        : one lane issues one TMA box per k range ([16 rows][64 k]); both warps split every 16-byte
 //                        unit into hi and lo and move it to its place in the two K-major core-matrix operand images
 //   split warps (8)    : thread = one TMEM lane = one output column; warp w owns lane quarter w % 4 and k half
 //                        w / 4 of every step: shared loads -> hi/lo -> tcgen05.st into the stage's hi and lo columns
-//   MMA warps (8)      : one lane each.  A warp gets a tcgen05.mma out only every ~118 cycles whatever the shape,
+//   MMA warps (4)      : one lane each.  A warp gets a tcgen05.mma out only every ~118 cycles whatever the shape,
 //                        but warps issue side by side (measured: 8 warps, one MMA per 15 cycles in aggregate), so
-//                        each of the 8 k blocks of a step has its own issuer (3 MMAs) and its own accumulators;
-//                        S = 4 needs 64 accumulator columns per issuer and runs with 4 issuers, 2 k blocks each
+//                        the 8 k blocks of a step are dealt round-robin to 4 issuers (3 MMAs per block), each with
+//                        its own accumulators
 //   split warps 0-3    : epilogue -- tcgen05.ld of the accumulators, fixed-order sum, bias, FP32 store
 // TMEM columns (512): (256 / issuers) i + 16 S a .. accumulator a of issuer i, 256 + 128 s .. stage s (64 hi columns, 64 lo).
 // Every wait is time-bounded; on a timeout the kernel raises a fault word, stops issuing work, and still frees
@@ -51,7 +53,7 @@ constexpr int kQuarterBytes = 32 * kStepK * 4;  // one lane quarter's tile: 32 c
 constexpr int kStepBytes = 4 * kQuarterBytes;
 constexpr int kStages = 2;                      // A stages in TMEM
 constexpr int kStageCols = 2 * kStepK;          // hi columns then lo columns
-constexpr int kMaxIssuers = 8;                  // 8 for S <= 2, 4 for S = 4
+constexpr int kMaxIssuers = 4;
 constexpr int kAccRegion = 256;                 // TMEM columns for accumulators: 256 / issuers each, 16 S per accumulator
 constexpr int kTmemCols = 512;
 constexpr int kTmemA = kAccRegion;
@@ -61,7 +63,7 @@ constexpr int kXHalf1 = 2 * kXSbo;              // hi (or lo) image of one k ran
 constexpr int kXRaw1 = 16 * kStepK * 4;         // one k range of [16 rows][64 k] as TMA lands it
 constexpr int kXBufs = 2;
 constexpr int kRedBytes = 128 * 16 * 4;         // k-range partials: [lane][16] floats
-constexpr int kWTma = 8, kWX0 = 9, kWMma0 = 11;  // warp roles; 0-7 split, 8 TMA, 9-10 x, 11-18 MMA
+constexpr int kWTma = 8, kWX0 = 12, kWMma0 = 14;  // warp roles; 0-7 split, 8-11 TMA, 12-13 x, 14-17 MMA
 constexpr int kThreads = (kWMma0 + kMaxIssuers) * 32;
 constexpr uint32_t kHiMask = 0xffffe000u;       // keeps sign, exponent and the 10 mantissa bits TF32 uses
 
@@ -81,10 +83,12 @@ __device__ __forceinline__ void split_tf32(uint32_t v, uint32_t& hi, uint32_t& l
 
 template <bool NK>
 __global__ void __launch_bounds__(kThreads, 1)
-gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
+gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap wmap2,
+               const __grid_constant__ CUtensorMap wmap3, const __grid_constant__ CUtensorMap wmap4,
+               const __grid_constant__ CUtensorMap xmap) {  // wmap2-4 (KN only): boxes 64, 96, 128 columns wide
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int S = a.split, kRing = a.ring;
-  const int issuers = S == 4 ? 4 : kMaxIssuers, acc_cols = kAccRegion / issuers;
+  const int issuers = kMaxIssuers, acc_cols = kAccRegion / issuers;
   const int kXHalfBytes = S * kXHalf1, kXBytes = 2 * kXHalfBytes, kXRawBytes = S * kXRaw1;
   unsigned char* ring = smem_raw;                            // [ring][kStepBytes]
   unsigned char* xbuf = ring + kRing * kStepBytes;           // [kXBufs][hi image | lo image], 16 S rows each
@@ -107,7 +111,7 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kRing; ++i) {
-      mbar_init(w_full + i, 1);
+      mbar_init(w_full + i, 4);   // one arrival (with its bytes) per TMA warp
       mbar_init(w_empty + i, 8);
     }
     for (int i = 0; i < kXBufs; ++i) {
@@ -128,29 +132,40 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == kWTma) {
-    // ------------------------------------------------------------ TMA producer: W tiles
+  if (warp >= kWTma && warp < kWX0) {
+    // ------------------------------------------------------------ TMA producers: W tiles, one lane quarter each
     if (lane == 0) {
+      const int lq = warp - kWTma;
       bool ok = true;
       while (ok && cur.begin_strip()) {
         const int qpk = 4 / cur.split;  // lane quarters per k range = units the strip can hold
+        const bool live = lq % qpk < cur.units;
+        const int col0 = (cur.unit + lq % qpk) * 32, k_range0 = (lq / qpk) * cur.kper;
         do {
           const int buf = cur.q % kRing;
           if (cur.q >= kRing && !mbar_wait(w_empty + buf, ((cur.q / kRing) - 1) & 1)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(w_full + buf, static_cast<unsigned>(cur.units * cur.split * kQuarterBytes));
-          for (int lq = 0; lq < 4; ++lq) {
-            if (lq % qpk >= cur.units) continue;
-            unsigned char* dst = ring + buf * kStepBytes + lq * kQuarterBytes;
-            const int col0 = (cur.unit + lq % qpk) * 32, k0 = (lq / qpk) * cur.kper + cur.kc * kStepK;
-            if (NK) {  // two [32 columns][32 k] boxes, 128-byte rows, swizzled
-              tma_box_2d(dst, &wmap, k0, col0, w_full + buf);
-              tma_box_2d(dst + kQuarterBytes / 2, &wmap, k0 + 32, col0, w_full + buf);
-            } else {   // [64 k][32 columns]
-              tma_box_2d(dst, &wmap, col0, k0, w_full + buf);
+          const int k0 = k_range0 + cur.kc * kStepK;
+          if (NK) {  // two [32 columns][32 k] boxes, 128-byte rows, swizzled
+            if (!live) {
+              mbar_arrive_cta(w_full + buf);
+              continue;
             }
+            mbar_expect_tx(w_full + buf, static_cast<unsigned>(kQuarterBytes));
+            unsigned char* dst = ring + buf * kStepBytes + lq * kQuarterBytes;
+            tma_box_2d(dst, &wmap, k0, col0, w_full + buf);
+            tma_box_2d(dst + kQuarterBytes / 2, &wmap, k0 + 32, col0, w_full + buf);
+          } else {   // the first quarter of each k range fetches [64 k][32 u columns] for all its quarters
+            if (lq % qpk != 0) {
+              mbar_arrive_cta(w_full + buf);
+              continue;
+            }
+            mbar_expect_tx(w_full + buf, static_cast<unsigned>(cur.units * kQuarterBytes));
+            unsigned char* dst = ring + buf * kStepBytes + lq * kQuarterBytes;
+            const CUtensorMap* map = cur.units == 1 ? &wmap : (cur.units == 2 ? &wmap2 : (cur.units == 3 ? &wmap3 : &wmap4));
+            tma_box_2d(dst, map, col0, k0, w_full + buf);
           }
         } while (cur.next_step());
       }
@@ -193,7 +208,7 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
       }
       if (!ok) atomicOr(&g_tc_fault, 2u);
     }
-  } else if (warp >= kWX0) {  // the two warps between the TMA warp and the MMA warps
+  } else if (warp >= kWX0) {  // the two warps between the TMA warps and the MMA warps
     // ------------------------------------------------------------ x warps
     const int t = threadIdx.x - kWX0 * 32;  // 0 .. 63
     bool ok = true;
@@ -260,13 +275,15 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
       const int col = (cur.unit + uq) * 32 + lane;
       const int split = cur.split;
       const int naccs = min(acc_cols / (16 * S), cur.steps);
+      const int pitch = cur.units * 32;  // KN: floats per k row of the tile
       do {
         const int buf = cur.q % kRing, s = cur.q % kStages;
         if (ok) ok = mbar_wait(w_full + buf, (cur.q / kRing) & 1);
         if (ok && cur.q >= kStages) ok = mbar_wait(a_empty + s, ((cur.q / kStages) - 1) & 1);
         if (ok && warp_live) {
           tc_fence_after();
-          const unsigned char* tile = ring + buf * kStepBytes + lq * kQuarterBytes;
+          // NK: this quarter's own tile; KN: the tile of its k range, [64 k][32 u columns], this quarter's columns at 32 uq
+          const unsigned char* tile = ring + buf * kStepBytes + (NK ? lq : lq - uq) * kQuarterBytes;
 #pragma unroll
           for (int g = 0; g < kStepK / 2 / 16; ++g) {  // 16 k at a time
             uint32_t hi[16], lo[16];
@@ -283,9 +300,9 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
                 split_tf32(v.w, hi[4 * p + 3], lo[4 * p + 3]);
               }
             } else {
-              const uint32_t* colp = reinterpret_cast<const uint32_t*>(tile) + (kh * (kStepK / 2) + g * 16) * 32 + lane;
+              const uint32_t* colp = reinterpret_cast<const uint32_t*>(tile) + (kh * (kStepK / 2) + g * 16) * pitch + uq * 32 + lane;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) split_tf32(colp[j * 32], hi[j], lo[j]);
+              for (int j = 0; j < 16; ++j) split_tf32(colp[j * pitch], hi[j], lo[j]);
             }
             tmem_st16(a_lane_base + s * kStageCols + g * 16, hi);
             tmem_st16(a_lane_base + s * kStageCols + kStepK + g * 16, lo);
@@ -365,17 +382,21 @@ int launch_tc(const float* x, const float* w, const float* bias, float* y, int m
   a.ring = static_cast<int>((220 * 1024 - fixed) / kStepBytes);
   if (a.ring > kMaxRing) a.ring = kMaxRing;
   const size_t smem = a.ring * static_cast<size_t>(kStepBytes) + fixed;
-  CUtensorMap wmap, xmap;
+  CUtensorMap wmaps[4], xmap;
+  CUtensorMap& wmap = wmaps[0];
   if (NK) {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(n)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 4};
     const cuuint32_t box[2] = {32, 32};
     if (!encode_tiled(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w, dims, strides, box, true)) return XDK_ERR_LAUNCH;
+    wmaps[1] = wmaps[2] = wmaps[3] = wmap;
   } else {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(n) * 4};
-    const cuuint32_t box[2] = {32, kStepK};
-    if (!encode_tiled(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w, dims, strides, box, false)) return XDK_ERR_LAUNCH;
+    for (int u = 1; u <= 4; ++u) {
+      const cuuint32_t box[2] = {static_cast<cuuint32_t>(32 * u), kStepK};
+      if (!encode_tiled(&wmaps[u - 1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w, dims, strides, box, false)) return XDK_ERR_LAUNCH;
+    }
   }
   // x[M][K] seen as [row][k range][k inside the range]: one box brings the 64-k step of every range
   const cuuint64_t xdims[3] = {static_cast<cuuint64_t>(k / a.split), static_cast<cuuint64_t>(a.split), static_cast<cuuint64_t>(m)};
@@ -385,7 +406,7 @@ int launch_tc(const float* x, const float* w, const float* bias, float* y, int m
   auto kernel = gemv_tc_kernel<NK>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return note_launch(err);
-  return launch(kernel, dim3(a.ctas), dim3(kThreads), smem, stream, 1u, a, wmap, xmap);
+  return launch(kernel, dim3(a.ctas), dim3(kThreads), smem, stream, 1u, a, wmaps[0], wmaps[1], wmaps[2], wmaps[3], xmap);
 }
 
 }  // namespace
