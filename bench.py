@@ -177,7 +177,7 @@ def main() -> None:
 
     from cross_dsl_kernels_b200 import kernel_bench, workloads as wl
     from cross_dsl_kernels_b200.ops import decode_linear
-    from cross_dsl_kernels_b200.timing import ClockSampler
+    from cross_dsl_kernels_b200.timing import ClockSampler, lockstep_replays
 
     # A multi-rank run that stalls (a peer that never joins, a collective that never completes) must not
     # sit until an outer limit kills it: after the budget every rank reports where it was and leaves.
@@ -244,9 +244,12 @@ def main() -> None:
             graph.replay()
         end.record()
         barrier()
-        # keep the sampler alive long enough to see the loaded clock when the timed region is short
-        t_end = time.perf_counter() + 1.0
-        while time.perf_counter() < t_end:
+        # Keep the sampler alive for about a second of load so that it sees the loaded clock when the timed region
+        # is short.  At N > 1 the step graph holds collectives, so every rank must replay it the same number of
+        # times: the count comes from the slowest rank's measured step time, never from a rank's own wall clock
+        # (ranks that stop at different counts leave the others waiting in a collective for ever).
+        extra = lockstep_replays(start.elapsed_time(end), args.steps)
+        for _ in range(extra):
             graph.replay()
         torch.cuda.synchronize()
     mark("sweep timed")

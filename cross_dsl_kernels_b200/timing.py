@@ -70,6 +70,22 @@ def graph_median_us(calls: Sequence[Callable[[], object]], replays: int = 20, wa
     }
 
 
+def lockstep_replays(local_ms: float, steps: int, *, device="cuda", group=None, target_ms: float = 1000.0,
+                     cap: int = 5000) -> int:
+    """How many extra replays of a step graph give about ``target_ms`` of load -- the SAME number on every rank.
+
+    A step graph that holds collectives must be replayed equally often by all ranks: a rank that stops early
+    leaves the others waiting in a collective for ever.  So the count is derived from the slowest rank's
+    measured time for ``steps`` replays (MAX all-reduce), never from a rank's own wall clock."""
+    import torch.distributed as dist
+
+    ms = torch.tensor([float(local_ms)], device=device, dtype=torch.float64)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=group)
+    per_step = max(float(ms.item()), 1e-3) / max(1, steps)
+    return int(min(float(cap), max(1.0, target_ms / per_step)))
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
 

@@ -56,3 +56,31 @@ def test_column_sharding_with_two_gloo_ranks():
     ok = mp.get_context("spawn").Array("i", [0] * world)
     mp.spawn(_worker, args=(world, _free_port(), ok), nprocs=world, join=True)
     assert list(ok) == [1] * world
+
+
+def _replay_count_worker(rank: int, world: int, port: int, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cross_dsl_kernels_b200.timing import lockstep_replays
+        # the ranks measured different times for the same 20 steps; both must replay the graph equally often
+        out[rank] = lockstep_replays(7.0 if rank == 0 else 9.5, 20, device="cpu")
+        out[world + rank] = lockstep_replays(1e-9 * (rank + 1), 20, device="cpu")  # absurdly fast: capped
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_agree_on_the_number_of_graph_replays():
+    """A step graph with collectives inside must be replayed the same number of times on every rank; the
+    count follows the slowest rank's step time (about one second of load), and is bounded."""
+    world = 2
+    out = mp.get_context("spawn").Array("i", [0] * (2 * world))
+    mp.spawn(_replay_count_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert out[0] == out[1] == int(1000.0 / (9.5 / 20))
+    assert out[2] == out[3] == 5000
+
+
+def test_replay_count_without_a_process_group():
+    from cross_dsl_kernels_b200.timing import lockstep_replays
+    assert lockstep_replays(10.0, 20, device="cpu") == 2000
+    assert lockstep_replays(1e6, 2, device="cpu") == 1
