@@ -27,6 +27,7 @@ SIGNATURES = {
     "xdk_fault_flags": (ctypes.c_uint, []),
     "xdk_rmsnorm": (_int, [_p, _p, _p, _p, _p, _i64, _i64, ctypes.c_float, _int, _p]),
     "xdk_gemv_f32": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, ctypes.c_size_t, _p]),
+    "xdk_gemv_tc_plan": (_int, [_i64, _i64, _i64, _int, _p]),
     "xdk_gemv_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _int]),
     "xdk_gemv_f32_static_scratch": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _p]),
     "xdk_rope_kv_append": (_int, [_p] * 11 + [_i64] * 11 + [_int, _int, _int, _p]),

@@ -35,6 +35,7 @@ unsigned w4a16_fault_word();
 // tcgen05 FP32 projection (gemv_tc.cu): whether it takes the shape, and its launch
 bool gemv_tc_eligible(const float* x, const float* w, int64_t m, int64_t k, int64_t n, bool nk);
 int launch_gemv_tc(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, bool nk, cudaStream_t stream);
+bool gemv_tc_plan(int64_t m, int64_t k, int64_t n, bool nk, int32_t out[5]);  // {CTAs, K split, ring depth, smem bytes, units}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

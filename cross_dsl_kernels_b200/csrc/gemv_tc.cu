@@ -369,10 +369,8 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
   }
 }
 
-template <bool NK>
-int launch_tc(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, cudaStream_t stream) {
-  TcArgs a;
-  a.bias = bias, a.y = y, a.m = m, a.k = k, a.n = n;
+// Grid, K split, ring depth and dynamic shared memory of a launch (fills a.total_units, a.ctas, a.split, a.ring).
+size_t plan_tc(TcArgs& a, int k, int n) {
   a.total_units = (n + 31) / 32;
   a.ctas = a.total_units < sm_count() ? a.total_units : sm_count();
   const int per_cta = (a.total_units + a.ctas - 1) / a.ctas;
@@ -381,7 +379,14 @@ int launch_tc(const float* x, const float* w, const float* bias, float* y, int m
   const size_t fixed = kXBufs * static_cast<size_t>(a.split) * (2 * kXHalf1 + kXRaw1) + kRedBytes + 64 * sizeof(uint64_t);
   a.ring = static_cast<int>((220 * 1024 - fixed) / kStepBytes);
   if (a.ring > kMaxRing) a.ring = kMaxRing;
-  const size_t smem = a.ring * static_cast<size_t>(kStepBytes) + fixed;
+  return a.ring * static_cast<size_t>(kStepBytes) + fixed;
+}
+
+template <bool NK>
+int launch_tc(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, cudaStream_t stream) {
+  TcArgs a;
+  a.bias = bias, a.y = y, a.m = m, a.k = k, a.n = n;
+  const size_t smem = plan_tc(a, k, n);
   CUtensorMap wmaps[4], xmap;
   CUtensorMap& wmap = wmaps[0];
   if (NK) {
@@ -420,6 +425,15 @@ bool gemv_tc_eligible(const float* x, const float* w, int64_t m, int64_t k, int6
 
 int launch_gemv_tc(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, bool nk, cudaStream_t stream) {
   return nk ? launch_tc<true>(x, w, bias, y, m, k, n, stream) : launch_tc<false>(x, w, bias, y, m, k, n, stream);
+}
+
+bool gemv_tc_plan(int64_t m, int64_t k, int64_t n, bool nk, int32_t out[5]) {
+  alignas(16) static const float aligned_dummy[4] = {0, 0, 0, 0};
+  if (!gemv_tc_eligible(aligned_dummy, aligned_dummy, m, k, n, nk)) return false;
+  TcArgs a;
+  const size_t smem = plan_tc(a, static_cast<int>(k), static_cast<int>(n));
+  out[0] = a.ctas, out[1] = a.split, out[2] = a.ring, out[3] = static_cast<int32_t>(smem), out[4] = a.total_units;
+  return true;
 }
 
 unsigned gemv_tc_fault_word() {
