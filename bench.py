@@ -19,7 +19,10 @@ over NCCL inside the same graph (strong scaling: the job is the same).
 Additional keys on the JSON line: ``kernels`` (CUDA-graph per-call median and
 achieved GB/s of every kernel at the BASELINE shapes, the metric upstream
 reports), ``chain`` (the Llama-3-8B-shaped decode-layer chain), ``roofline``,
-``cpu_baseline``, ``e2e``, ``clocks``.
+``cpu_baseline``, ``e2e``, ``clocks``.  ``e2e`` is the same sweep with every
+projection's x copied from pinned host memory and its y copied back, all inside
+one CUDA graph per step (copy nodes on two forked streams), timed by wall clock
+around replay + host synchronize.
 
 ``--impl reference`` times the CPU restatement of upstream's PyTorch reference
 (oracle/, the same torch ops upstream's reference functions call) on the
