@@ -51,16 +51,18 @@ def bench_rmsnorm(rows: int, hidden: int, dtype, peak=None, replays=20) -> dict:
     return _row(name, nbytes, t, sets, peak)
 
 
-def bench_gemv(m: int, k: int, n: int, layout: str, split_k: int = 0, bias=True, peak=None, replays=20) -> dict:
+def bench_gemv(m: int, k: int, n: int, layout: str, split_k: int = 0, bias=True, peak=None, replays=20,
+               strict_fp32: bool = False) -> dict:
     nbytes = wl.projection_bytes(m, k, n, bias)
     sets = rotation_for(nbytes, cap=8)
     x, w, b = wl.projection_inputs(m, k, n, layout, bias)
     xd, bd = x.cuda(), (b.cuda() if bias else None)
     ws = [w.cuda()] + [torch.empty_like(w, device="cuda").normal_(0, k ** -0.5) for _ in range(sets - 1)]
     ncalls = _calls_per_graph(sets)
-    calls = [(lambda wt=ws[i % sets]: decode_linear(xd, wt, bd, weight_layout=layout, split_k=split_k)) for i in range(ncalls)]
+    calls = [(lambda wt=ws[i % sets]: decode_linear(xd, wt, bd, weight_layout=layout, split_k=split_k, strict_fp32=strict_fp32)) for i in range(ncalls)]
     t = graph_median_us(calls, replays)
-    return _row(f"gemv_f32_{layout}_m{m}_k{k}_n{n}_s{split_k}", nbytes, t, sets, peak, split_k=split_k)
+    name = f"gemv_f32_{layout}_m{m}_k{k}_n{n}_s{split_k}" + ("_strict" if strict_fp32 else "")
+    return _row(name, nbytes, t, sets, peak, split_k=split_k)
 
 
 def bench_rope(dtype, layout: str, rope_dim: int, peak=None, replays=20, **shape) -> dict:
@@ -148,14 +150,15 @@ def table(which=("rmsnorm", "gemv", "rope", "w4a16"), peak=None, split_sweep=Tru
 
 
 def one(argv: list[str]) -> dict:
-    """``--one rmsnorm ROWS HIDDEN f32|bf16|f16`` | ``--one gemv M K N KN|NK SPLIT`` |
+    """``--one rmsnorm ROWS HIDDEN f32|bf16|f16`` | ``--one gemv M K N KN|NK SPLIT [strict]`` |
     ``--one rope f32|bf16 NHD|HND ROPE_DIM`` | ``--one w4a16 M K N GROUP``; few replays (for profilers)."""
     dtypes = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
     op, rest = argv[0], argv[1:]
     if op == "rmsnorm":
         return bench_rmsnorm(int(rest[0]), int(rest[1]), dtypes[rest[2]], replays=3)
     if op == "gemv":
-        return bench_gemv(int(rest[0]), int(rest[1]), int(rest[2]), rest[3], int(rest[4]), replays=3)
+        return bench_gemv(int(rest[0]), int(rest[1]), int(rest[2]), rest[3], int(rest[4]), replays=3,
+                          strict_fp32=len(rest) > 5 and rest[5] == "strict")
     if op == "rope":
         return bench_rope(dtypes[rest[0]], rest[1], int(rest[2]), replays=3)
     if op == "w4a16":
