@@ -135,6 +135,8 @@ def table(which=("rmsnorm", "gemv", "rope", "w4a16"), peak=None, split_sweep=Tru
                 for m in (1, 4, 16):
                     for s in ((0, 1, 2, 4, 8) if split_sweep else (0,)):
                         rows.append(bench_gemv(m, 4096, n, layout, s, True, peak))
+                if n == 14336:  # the strict-FP32 alternative of the tensor-core path, for comparison
+                    rows.append(bench_gemv(16, 4096, n, layout, 0, True, peak, strict_fp32=True))
     if "rope" in which:
         for dtype in (torch.float32, torch.bfloat16):
             for layout in ("NHD", "HND"):
