@@ -1,28 +1,39 @@
 """Benchmark of the B200 decode kernels.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-table]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-table] [--exchange peer|nccl]
 
-Headline workload (``config.workload``): the FP32 decode projection sweep of
-the second BASELINE configuration -- y = xW + b for M in {1,4,16}, K = 4096,
-N in {4096, 14336}, weights stored KN and NK: twelve projections per step, each
-with the split-K factor the library picks.  One "step" is one pass over the
-twelve; ``value`` is the sweep's algorithmic bytes (every operand read or
-written once) divided by the device time of a step, in GB/s, measured by
-replaying a CUDA graph of the step with the weights resident in HBM.  The step
-touches 604 MB of weights in an order that never reuses a matrix within 500 MB
-of other traffic, so no call is served from the 126 MB L2.
+Headline workload (``config.workload``): the FP32 decode projection sweep --
+y = xW + b for M in {1,4,16}, K = 4096, N in {4096, 14336}, weights stored KN
+and NK: twelve projections per step, each with the split-K factor the library
+picks.  One "step" is one pass over the twelve; ``value`` is the sweep's
+algorithmic bytes (every operand read or written once) divided by the device
+time of a step, in GB/s, measured by replaying a CUDA graph of the step with
+the weights resident in HBM.  The step touches 604 MB of weights in an order
+that never reuses a matrix within 500 MB of other traffic, so no call is
+served from the 126 MB L2.
 
 With N > 1 GPUs (launched by torchrun, one rank per GPU) every projection is
-column-sharded: rank r owns N/g output columns and the shards are all-gathered
-over NCCL inside the same graph (strong scaling: the job is the same).
+column-sharded: rank r owns N/g output columns and its kernel stores them into
+the full-width result on every rank from its epilogue (peer-mapped memory over
+NVLink), with one flag barrier per step; ``--exchange nccl`` runs the
+comparison arm instead (one NCCL all-gather and one re-layout kernel per
+projection).  Strong scaling: the job is the same at every N.
+
+Every number is gated before it is timed: the step's results are compared with
+an FP64 product (the projection's own tolerance), once eagerly and once more
+after a graph replay whose outputs were filled with NaN first; at N > 1 the
+gate runs on the gathered full-width result of every rank.  A failed gate ends
+the run with a non-zero exit code.
 
 Additional keys on the JSON line: ``kernels`` (CUDA-graph per-call median and
-achieved GB/s of every kernel at the BASELINE shapes, the metric upstream
-reports), ``chain`` (the Llama-3-8B-shaped decode-layer chain), ``roofline``,
-``cpu_baseline``, ``e2e``, ``clocks``.  ``e2e`` is the same sweep with every
-projection's x copied from pinned host memory and its y copied back, all inside
-one CUDA graph per step (copy nodes on two forked streams), timed by wall clock
-around replay + host synchronize.
+achieved GB/s of every kernel at its headline shapes, each gated against the
+CPU oracle -- eager, poisoned replay, changed-input replay -- with the CPU
+reference path timed beside it), ``chain`` (the Llama-3-8B-shaped decode-layer
+chain), ``roofline``, ``cpu_baseline``, ``e2e``, ``clocks``, ``spread``.
+``e2e`` is the same sweep with every projection's x copied from pinned host
+memory and the full-width y copied back, all inside one CUDA graph per step
+(copy nodes on two forked streams), timed by wall clock around replay + host
+synchronize.
 
 ``--impl reference`` times the CPU restatement of upstream's PyTorch reference
 (oracle/, the same torch ops upstream's reference functions call) on the
@@ -63,6 +74,16 @@ def measured_peaks() -> dict:
         data = json.loads(path.read_text())
         return {"hbm_gbs": float(data["hbm_gbs"]), "source": "measured"}
     return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def profile_traffic(name: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch, from the machine-readable copy of an ncu summary
+    (profiles/<name>.json, written next to the .md when the capture was read); None when there is none."""
+    path = ROOT / "profiles" / f"{name}.json"
+    if not path.exists():
+        return None
+    data = json.loads(path.read_text())
+    return int(data["dram_bytes_read"]) + int(data["dram_bytes_write"])
 
 
 # ------------------------------------------------------------------------------------------------
@@ -118,18 +139,188 @@ def run_reference(args, rank: int) -> None:
         "impl": "reference", "metric": METRIC, "value": round(res["value"], 3), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": res["steps_timed"], "warmup": args.warmup, "ms_per_step": round(res["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "config": workload_config(args.gpus, args.exchange),
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": round(res["value"], 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(gpus: int) -> dict:
+def workload_config(gpus: int, exchange: str) -> dict:
+    how = {"peer": "epilogue stores into every rank's peer-mapped full-width y + one flag barrier per step",
+           "nccl": "NCCL all-gather of y + re-layout kernel per projection"}[exchange]
     return {"workload": "fp32 decode projection sweep: M in {1,4,16} x N in {4096,14336} x {KN,NK}, K=4096, bias, split_k auto",
             "projections_per_step": len(SWEEP), "bytes_per_step": sweep_bytes(),
             "l2_policy": "inputs larger than L2: 604 MB of weights per step, no matrix reused within 500 MB",
-            "parallelism": "single GPU" if gpus == 1 else f"N-column sharding over {gpus} GPUs + NCCL all-gather of y"}
+            "parallelism": "single GPU" if gpus == 1 else f"N-column sharding over {gpus} GPUs; {how}"}
+
+
+# ------------------------------------------------------------------------------------------------
+# gates and CPU timings of the per-kernel table (the oracle is the checker here, never the thing shipped)
+
+
+def _median_cpu_us(fn, budget_s: float = 2.5, min_runs: int = 3, max_runs: int = 10) -> float:
+    fn()
+    times, t_begin = [], time.perf_counter()
+    while len(times) < max_runs and (len(times) < min_runs or time.perf_counter() - t_begin < budget_s):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times) * 1e6
+
+
+def _rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
+    return float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-12))
+
+
+def _ulps16(a: torch.Tensor, b: torch.Tensor) -> int:
+    def ordered(t):
+        bits = t.contiguous().view(torch.int16).to(torch.int32)
+        return torch.where(bits < 0, -(bits & 0x7FFF), bits)
+    return int((ordered(a) - ordered(b)).abs().max())
+
+
+class GateFailure(AssertionError):
+    pass
+
+
+def _need(ok: bool, what: str) -> None:
+    if not ok:
+        raise GateFailure(what)
+
+
+def rmsnorm_row(kb, rows, hidden, dtype, peak, dependent=False):
+    from cross_dsl_kernels_b200 import workloads as wl
+    from oracle import decode_ops
+
+    x, r, w = wl.rmsnorm_inputs(rows, hidden, dtype)
+
+    def check(stage, out):
+        xin = -x if stage == "changed" else x
+        want_y, want_r = decode_ops.residual_rmsnorm(xin, r, w, 1e-6)
+        y, ro = out[0].cpu(), out[1].cpu()
+        _need(torch.equal(ro, want_r), f"rmsnorm {stage}: residual_out is not bit-exact")
+        if dtype == torch.float32:
+            _need(_rel_l2(y, want_y) <= 1e-5 and float((y - want_y).abs().max()) <= 2e-5, f"rmsnorm {stage}: y outside 1e-5")
+        else:
+            _need(_ulps16(y, want_y) <= 1, f"rmsnorm {stage}: y more than one ulp off")
+
+    row = kb.bench_rmsnorm(rows, hidden, dtype, peak, check=check, dependent=dependent)
+    if not dependent:
+        row["cpu_us"] = round(_median_cpu_us(lambda: decode_ops.residual_rmsnorm(x, r, w, 1e-6)), 1)
+    return row
+
+
+def gemv_row(kb, m, n, layout, split_k, peak, strict=False, dependent=False, cpu=True):
+    from cross_dsl_kernels_b200 import workloads as wl
+    from cross_dsl_kernels_b200.tolerances import fp32_gemv_tolerance
+    from oracle import decode_ops
+
+    x, w, b = wl.projection_inputs(m, K, n, layout, True)
+    w_kn = w if layout == "KN" else w.t()
+    want = x.double() @ w_kn.double()
+    tol = fp32_gemv_tolerance(K)
+
+    def check(stage, out):
+        ref = (-want if stage == "changed" else want) + b.double()
+        y = out.cpu().double()
+        _need(float((y - ref).abs().max()) <= tol["max_abs_err"], f"gemv {layout} m{m} n{n} s{split_k} {stage}: max abs error")
+        _need(_rel_l2(y, ref) <= tol["rel_l2_err"], f"gemv {layout} m{m} n{n} s{split_k} {stage}: rel-L2 error")
+
+    row = kb.bench_gemv(m, K, n, layout, split_k, True, peak, strict_fp32=strict, check=check, dependent=dependent)
+    if cpu:
+        row["cpu_us"] = round(_median_cpu_us(lambda: decode_ops.decode_projection(x, w, b, weight_layout=layout)), 1)
+    return row
+
+
+def rope_row(kb, dtype, layout, rope_dim, peak, dependent=False):
+    from cross_dsl_kernels_b200 import workloads as wl
+    from oracle import decode_ops
+
+    case = wl.rope_inputs(rope_dim=rope_dim, layout=layout, dtype=dtype)
+    tokens, hkv, dim, ps = case["q"].shape[0], case["k"].shape[1], case["q"].shape[2], case["page_size"]
+    # The oracle runs on a compact cache: the pages the batch touches, renumbered 0 .. tokens-1.
+    logical = case["positions"] // ps
+    used = case["page_table"][case["sequence_ids"], logical]            # physical page of every token
+    compact_table = torch.zeros_like(case["page_table"])
+    compact_table[case["sequence_ids"], logical] = torch.arange(tokens)
+    small = (tokens, ps, hkv, dim) if layout == "NHD" else (tokens, hkv, ps, dim)
+
+    def oracle(sign):
+        kc, vc = torch.full(small, -999.0, dtype=dtype), torch.full(small, -999.0, dtype=dtype)
+        q = decode_ops.rope_paged_append(sign * case["q"], sign * case["k"], sign * case["v"], case["cos"], case["sin"],
+                                         case["positions"], compact_table, case["sequence_ids"], kc, vc, page_size=ps,
+                                         rope_dim=rope_dim, interleaved=False, kv_layout=layout)
+        return q, kc, vc
+
+    def check(stage, out):
+        q_want, kc_want, vc_want = oracle(-1 if stage == "changed" else 1)
+        q_out, kc, vc = out
+        _need(torch.equal(q_out.cpu(), q_want), f"rope {stage}: rotated Q is not bit-exact")
+        for got, want, which in ((kc, kc_want, "K"), (vc, vc_want, "V")):
+            _need(torch.equal(got[used.cuda()].cpu(), want), f"rope {stage}: {which} pages are not bit-exact")
+            _need(int((got != -999.0).sum()) == tokens * hkv * dim, f"rope {stage}: {which} cache touched outside its slots")
+
+    row = kb.bench_rope(dtype, layout, rope_dim, peak, check=check, dependent=dependent)
+    if not dependent:
+        row["cpu_us"] = round(_median_cpu_us(lambda: oracle(1)), 1)                      # batched form (upstream :106-149)
+        flat = lambda: decode_ops.rope_paged_append_flat(                                # token-by-token form (upstream :35-70)
+            case["q"], case["k"], case["v"], case["cos"], case["sin"], case["positions"], compact_table, case["sequence_ids"],
+            torch.full(small, -999.0, dtype=dtype), torch.full(small, -999.0, dtype=dtype), page_size=ps, rope_dim=rope_dim,
+            interleaved=False, kv_layout=layout)
+        row["cpu_loop_us"] = round(_median_cpu_us(flat), 1)
+    return row
+
+
+def w4a16_row(kb, m, n, peak, dependent=False):
+    from cross_dsl_kernels_b200 import workloads as wl
+    from oracle import int4
+
+    x, packed, scales, _ = wl.w4a16_inputs(m, K, n, 128)
+    want = int4.w4a16_projection(x, packed, scales, None, group_size=128).double()
+
+    def check(stage, out):
+        ref = -want if stage == "changed" else want
+        y = out.cpu().double()
+        _need(bool(((y - ref).abs() <= 0.002 + 0.002 * ref.abs()).all()), f"w4a16 m{m} n{n} {stage}: element gate")
+        _need(_rel_l2(y, ref) <= 1e-3, f"w4a16 m{m} n{n} {stage}: rel-L2")
+
+    row = kb.bench_w4a16(m, K, n, 128, peak, check=check, dependent=dependent)
+    if not dependent:
+        row["cpu_us"] = round(_median_cpu_us(lambda: int4.w4a16_projection(x, packed, scales, None, group_size=128), budget_s=3.0), 1)
+        dense = int4.dequantize(packed, scales, K, 128).float()
+        xf = x.float()
+        row["cpu_dense_us"] = round(_median_cpu_us(lambda: xf @ dense.t()), 1)           # pre-dequantised dense comparator
+    return row
+
+
+def gated_table(kb, peak: float) -> list[dict]:
+    rows = [kb.bench_noop(), kb.bench_noop(dependent=True)]
+    for dtype in (torch.float32, torch.bfloat16):
+        for r in (256, 4096):
+            rows.append(rmsnorm_row(kb, r, 4096, dtype, peak))
+    rows.append(rmsnorm_row(kb, 256, 4096, torch.bfloat16, peak, dependent=True))
+    for layout in ("KN", "NK"):
+        for n in (4096, 14336):
+            for m in (1, 4, 16):
+                for s in (0, 1, 2, 4, 8):
+                    rows.append(gemv_row(kb, m, n, layout, s, peak, cpu=(s == 0)))
+            if n == 14336:  # the strict-FP32 alternative of the tensor-core path, for comparison
+                rows.append(gemv_row(kb, 16, n, layout, 0, peak, strict=True, cpu=False))
+    for dtype in (torch.float32, torch.bfloat16):
+        for layout in ("NHD", "HND"):
+            for rd in (64, 128):
+                rows.append(rope_row(kb, dtype, layout, rd, peak))
+    rows.append(rope_row(kb, torch.bfloat16, "NHD", 128, peak, dependent=True))
+    for n in (4096, 14336):
+        for m in (1, 16):
+            rows.append(w4a16_row(kb, m, n, peak))
+            rows.append(w4a16_row(kb, m, n, peak, dependent=True))
+    cores = torch.get_num_threads()
+    for row in rows:
+        if "cpu_us" in row:
+            row["cpu_cores"] = cores
+    return rows
 
 
 # ------------------------------------------------------------------------------------------------
@@ -144,8 +335,10 @@ def mark(text: str) -> None:
 
 def build_gpu_sweep(rank: int, world: int):
     """Device tensors for this rank's column shard of every projection (drawn on the device: the same
-    Philox stream on every rank, so the shards are slices of one matrix)."""
-    weights = {}
+    Philox stream on every rank, so the shards are slices of one matrix) and the FP64 products the gate uses."""
+    weights, want = {}, {}
+    xs_host = {m: torch.randn(m, K, generator=torch.Generator().manual_seed(m)).pin_memory() for m in (1, 4, 16)}
+    xs = {m: t.cuda() for m, t in xs_host.items()}
     for n in (4096, 14336):
         g = torch.Generator(device="cuda").manual_seed(n)
         w = torch.randn(K, n, generator=g, device="cuda") / K ** 0.5
@@ -153,10 +346,11 @@ def build_gpu_sweep(rank: int, world: int):
         lo, hi = rank * n // world, (rank + 1) * n // world
         weights[(n, "KN")] = (w[:, lo:hi].contiguous(), b[lo:hi].contiguous())
         weights[(n, "NK")] = (w.t()[lo:hi].contiguous(), b[lo:hi].contiguous())
-        del w
-    xs_host = {m: torch.randn(m, K, generator=torch.Generator().manual_seed(m)).pin_memory() for m in (1, 4, 16)}
-    xs = {m: t.cuda() for m, t in xs_host.items()}
-    return xs_host, xs, weights
+        wd = w.double()
+        for m in (1, 4, 16):
+            want[(m, n)] = (xs[m].double() @ wd + b.double()).cpu()  # full width: what every rank must end up holding
+        del w, wd
+    return xs_host, xs, weights, want
 
 
 def main() -> None:
@@ -165,6 +359,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="how column shards reach every rank at N > 1")
     ap.add_argument("--no-table", action="store_true", help="skip the per-kernel table and the chain")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
@@ -178,9 +373,11 @@ def main() -> None:
 
     import torch.distributed as dist
 
-    from cross_dsl_kernels_b200 import kernel_bench, workloads as wl
+    from cross_dsl_kernels_b200 import _native, kernel_bench
+    from cross_dsl_kernels_b200.chain import unshard_columns
     from cross_dsl_kernels_b200.ops import decode_linear
     from cross_dsl_kernels_b200.timing import ClockSampler, lockstep_replays
+    from cross_dsl_kernels_b200.tolerances import fp32_gemv_tolerance
 
     # A multi-rank run that stalls (a peer that never joins, a collective that never completes) must not
     # sit until an outer limit kills it: after the budget every rank reports where it was and leaves.
@@ -199,37 +396,76 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         mark("process group ready")
     peaks = measured_peaks()
-    xs_host, xs, weights = build_gpu_sweep(rank, world)
+    xs_host, xs, weights, want = build_gpu_sweep(rank, world)
     mark("sweep weights on device")
-    # own kernels per step: one per projection (cluster kernels for M <= 4, the tcgen05 kernel for M = 16)
-    launches_per_step = len(SWEEP)
+    peer = world > 1 and args.exchange == "peer"
+    # own kernels per step: one per projection (cluster kernels for M <= 4, the tcgen05 kernel for M = 16),
+    # plus the flag barrier (peer) or the twelve re-layout kernels (nccl) at N > 1
+    launches_per_step = len(SWEEP) + (1 if peer else (len(SWEEP) if world > 1 else 0))
 
-    gathered = {}
-    if world > 1:
+    arena = site = None
+    full, gathered = {}, {}
+    if peer:
+        from cross_dsl_kernels_b200.peer import PeerArena
+
+        arena = PeerArena(sum(4 * m * n + 256 for m, n, _ in SWEEP) + 4096)
+        site = arena.new_site()
+        for key in SWEEP:
+            full[key] = arena.matrix(key[0], key[1], torch.float32)
+    elif world > 1:
         for m, n, layout in SWEEP:
             gathered[(m, n, layout)] = torch.empty(world, m, n // world, device="cuda")
+            full[(m, n, layout)] = torch.empty(m, n, device="cuda")
 
     def step():
+        """The twelve projections; returns the full-width result of each (on every rank)."""
         outs = []
-        for m, n, layout in SWEEP:
+        for key in SWEEP:
+            m, n, layout = key
             w, b = weights[(n, layout)]
-            y = decode_linear(xs[m], w, b, weight_layout=layout)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[(m, n, layout)], y)
-            outs.append(y)
+            if peer:
+                decode_linear(xs[m], w, b, weight_layout=layout, peer_out=full[key].out_for(rank * n // world))
+                outs.append(full[key].local)
+            else:
+                y = decode_linear(xs[m], w, b, weight_layout=layout)
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered[key], y)
+                    y = unshard_columns(gathered[key], full[key])
+                outs.append(y)
+        if peer:
+            arena.barrier(site)
         return outs
+
+    tol = fp32_gemv_tolerance(K)
+
+    def gate(outs, stage: str) -> None:
+        for (m, n, layout), y in zip(SWEEP, outs):
+            ref = want[(m, n)]
+            got = y.cpu().double()
+            ok = float((got - ref).abs().max()) <= tol["max_abs_err"] and _rel_l2(got, ref) <= tol["rel_l2_err"]
+            if not ok:
+                raise GateFailure(f"sweep {stage}: projection m{m} n{n} {layout} on rank {rank} of {world} is outside the gate")
 
     stream = torch.cuda.Stream()
     stream.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(stream):
         for _ in range(2):
-            step()
+            outs = step()
     stream.synchronize()
-    mark("sweep warmed up")
+    gate(outs, "eager")
+    mark("sweep warmed up and gated")
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=stream):
-        step()
-    mark("sweep captured")
+        outs = step()
+    for y in outs:  # a replay must rewrite every output
+        y.fill_(float("nan"))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    graph.replay()
+    torch.cuda.synchronize()
+    gate(outs, "poisoned replay")
+    mark("sweep captured and gated again")
 
     def barrier():
         if world > 1:
@@ -239,36 +475,42 @@ def main() -> None:
     for _ in range(args.warmup):
         graph.replay()
     barrier()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    blocks = 5  # every block: exactly `steps` replays between a barrier + synchronize on both sides
+    block_ms = []
     with ClockSampler(local_rank) as sampler:
-        barrier()
-        start.record()
-        for _ in range(args.steps):
-            graph.replay()
-        end.record()
-        barrier()
+        for _ in range(blocks):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            start.record()
+            for _ in range(args.steps):
+                graph.replay()
+            end.record()
+            barrier()
+            block_ms.append(start.elapsed_time(end))
         # Keep the sampler alive for about a second of load so that it sees the loaded clock when the timed region
-        # is short.  At N > 1 the step graph holds collectives, so every rank must replay it the same number of
-        # times: the count comes from the slowest rank's measured step time, never from a rank's own wall clock
-        # (ranks that stop at different counts leave the others waiting in a collective for ever).
-        extra = lockstep_replays(start.elapsed_time(end), args.steps)
+        # is short.  At N > 1 the step graph synchronises the ranks, so every rank must replay it the same number of
+        # times: the count comes from the slowest rank's measured step time, never from a rank's own wall clock.
+        extra = lockstep_replays(statistics.median(block_ms), args.steps)
         for _ in range(extra):
             graph.replay()
         torch.cuda.synchronize()
     mark("sweep timed")
-    elapsed_ms = torch.tensor([start.elapsed_time(end)], device="cuda")
+    per_block = torch.tensor(block_ms, device="cuda", dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(elapsed_ms.item()) / args.steps
+        dist.all_reduce(per_block, op=dist.ReduceOp.MAX)  # every block: the slowest rank
+    per_step = sorted((per_block / args.steps).tolist())
+    ms_per_step = statistics.median(per_step)
     value = sweep_bytes() / (ms_per_step * 1e-3) * 1e-9
+    spread = {"blocks": blocks, "steps_per_block": args.steps, "ms_per_step_median": round(ms_per_step, 5),
+              "ms_per_step_min": round(per_step[0], 5), "ms_per_step_max": round(per_step[-1], 5)}
 
-    # ---- end to end through the public Python API: pinned host x in, y out, every step
-    y_host = {(m, n, layout): torch.empty(m, n // world, pin_memory=True) for m, n, layout in SWEEP}
+    # ---- end to end through the public Python API: pinned host x in, full-width y out, every step
+    y_host = {key: torch.empty(key[0], key[1], pin_memory=True) for key in SWEEP}
 
     # One CUDA graph per step: every projection's x comes from pinned host memory (H2D memcpy node), runs through
-    # the public op, and its y goes back to pinned host memory (D2H memcpy node).  The copies sit on two forked
-    # streams (one per direction) so that they overlap the other projections' kernels; the step ends with a
-    # host synchronize.
+    # the public op (at N > 1 followed by the exchange that assembles the full-width y on every rank), and the full
+    # y goes back to pinned host memory (D2H memcpy node).  The copies sit on two forked streams (one per direction)
+    # so that they overlap the other projections' kernels; the step ends with a host synchronize.
     h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
     x_dev = {i: torch.empty(m, K, device="cuda") for i, (m, _, _) in enumerate(SWEEP)}
     # same 12 projections, largest outputs first: the copy that is still in flight when the last kernel ends is a small one
@@ -285,16 +527,33 @@ def main() -> None:
                 ev = torch.cuda.Event()
                 ev.record(h2d_stream)
                 x_ready.append(ev)
+        results = []
         for pos, i in enumerate(order):
-            m, n, layout = SWEEP[i]
+            key = SWEEP[i]
+            m, n, layout = key
             w, b = weights[(n, layout)]
             main.wait_event(x_ready[pos])
-            y = decode_linear(x_dev[i], w, b, weight_layout=layout)
-            y_ready = torch.cuda.Event()
-            y_ready.record(main)
-            with torch.cuda.stream(d2h_stream):  # each result leaves while the next projection runs
-                d2h_stream.wait_event(y_ready)
-                y_host[(m, n, layout)].copy_(y, non_blocking=True)
+            if peer:
+                decode_linear(x_dev[i], w, b, weight_layout=layout, peer_out=full[key].out_for(rank * n // world))
+                results.append((key, full[key].local))
+            else:
+                y = decode_linear(x_dev[i], w, b, weight_layout=layout)
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered[key], y)
+                    y = unshard_columns(gathered[key], full[key])
+                results.append((key, y))
+            if not peer:  # each result leaves while the next projection runs
+                y_ready = torch.cuda.Event()
+                y_ready.record(main)
+                with torch.cuda.stream(d2h_stream):
+                    d2h_stream.wait_event(y_ready)
+                    y_host[key].copy_(results[-1][1], non_blocking=True)
+        if peer:  # the full-width results are complete on this rank only after the step's barrier
+            arena.barrier(site)
+            d2h_stream.wait_stream(main)
+            with torch.cuda.stream(d2h_stream):
+                for key, y in results:
+                    y_host[key].copy_(y, non_blocking=True)
         main.wait_stream(h2d_stream)
         main.wait_stream(d2h_stream)
 
@@ -311,6 +570,7 @@ def main() -> None:
 
     for _ in range(3):
         e2e_step()
+    gate([y_host[key] for key in SWEEP], "end to end")
     barrier()
     t0 = time.perf_counter()
     e2e_steps = max(5, min(args.steps, 50))
@@ -321,10 +581,12 @@ def main() -> None:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e = {"value": round(sweep_bytes() / float(e2e_s.item()) * 1e-9, 2), "unit": "GB/s",
            "h2d_bytes_per_step": sum(4 * m * K for m, _, _ in SWEEP),
-           "d2h_bytes_per_step": sum(4 * m * n // world for m, n, _ in SWEEP),
+           "d2h_bytes_per_step": sum(4 * m * n for m, n, _ in SWEEP),
            "ms_per_step": round(float(e2e_s.item()) * 1e3, 4),
-           "method": "per step: replay of one CUDA graph (12 x [H2D x from pinned host -> public op -> D2H y to pinned host], "
-                     "copies on two forked streams) + host synchronize; wall clock"}
+           "method": "per step: replay of one CUDA graph (12 x [H2D x from pinned host -> public op (+ exchange at N > 1) -> "
+                     "D2H of the full-width y to pinned host], copies on two forked streams) + host synchronize; wall clock; "
+                     "the copied-back results are gated"}
+    mark("end to end timed")
 
     # Roofline of the dominant kernel of the step (largest time share: the M=16, N=14336 projections run
     # by gemv_tc_kernel), timed live as a CUDA-graph per-call median over rotating weight sets.
@@ -334,54 +596,83 @@ def main() -> None:
                 "peak_source": peaks["source"], "frac_of_nominal_8tbs": dom["frac_of_8tbs"], "us_per_launch": dom["us"],
                 "algorithmic_bytes_per_launch": dom["bytes"],
                 # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at N=14336
-                # (profiles/gemv_tc_m16_k4096_n14336.md): 235.25 MB + 4.77 MB
-                "traffic": 240020224 if world == 1 else None,
+                "traffic": profile_traffic("gemv_tc_m16_k4096_n14336") if world == 1 else None,
                 "sweep_achieved": round(value / world, 2), "sweep_frac": round(value / world / peaks["hbm_gbs"], 4),
                 "note": "M=16 runs on the tensor cores (3 TF32 MMAs per k block, FP32 accumulate); bound by the per-step hand-offs of its warp-specialised pipeline, not by HBM; M<=4 kernels reach 0.83-1.00 of the measured peak, see kernels[]"}
 
     mark("dominant kernel timed")
-    chain_row = None
+    chain_rows = None
     if not args.no_table:
-        chain_row = kernel_bench.bench_chain(rank=rank, world=world, peak=peaks["hbm_gbs"])
+        chain_rows = []
+        modes = [(args.exchange, False), (args.exchange, True)]
+        if world > 1 and args.exchange == "peer":
+            modes.append(("nccl", False))  # the comparison arm, once
+        for exchange, dependent in modes:
+            chain_rows.append(kernel_bench.bench_chain(rank=rank, world=world, peak=peaks["hbm_gbs"], exchange=exchange,
+                                                       dependent=dependent, check=chain_gate(rank, world)))
+        mark("chain done")
 
-    mark("chain done")
-    if rank != 0:
-        finish(world)
-        return
-
+    faults = _native.fault_flags() | (arena.fault_flags() << 0 if arena is not None else 0)
+    if faults:
+        raise GateFailure(f"a bounded device-side wait gave up (flags {faults:#x})")
     clocks = sampler.summary()
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world),
-        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
-        "roofline": roofline,
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world, args.exchange),
+        "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "spread": spread,
+        "roofline": roofline, "gated": True,
     }
-    if chain_row is not None:
-        line["chain"] = chain_row
-    if world == 1:
+    if chain_rows is not None:
+        line["chain"] = chain_rows
+    if rank == 0 and world == 1:
         line["cpu_baseline"] = {k: v for k, v in time_cpu_sweep(20, 2, budget_s=20.0).items()
                                 if k in ("value", "unit", "cores", "kind", "sample")}
         if not args.no_table:
-            rows = kernel_bench.table(peak=peaks["hbm_gbs"], split_sweep=True)
-            line["kernels"] = rows
-    print(json.dumps(line), flush=True)
-    finish(world)
-
-
-def finish(world: int) -> None:
-    """Multi-rank exit: meet once more, then leave without tearing NCCL down (communicators that
-    CUDA graphs still reference do not always unwind cleanly; the process is ending anyway)."""
+            line["kernels"] = gated_table(kernel_bench, peaks["hbm_gbs"])
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    # orderly exit: drop the graphs (they reference the communicator and the arena), drain, then tear down
+    del graph, e2e_graph
+    torch.cuda.synchronize()
     if world > 1:
-        import torch.distributed as dist
-
-        torch.cuda.synchronize()
         dist.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
+        if arena is not None:
+            arena.close()
+        dist.destroy_process_group()
+
+
+def chain_gate(rank: int, world: int):
+    """Gate of the decode-layer chain: at one GPU every stage of the last layer against the CPU oracle fed with the
+    kernel's own inputs; at N > 1 the assembled rotated Q and up+gate against the same chain run unsharded here."""
+    def check(chain, out):
+        from cross_dsl_kernels_b200.chain import DecodeLayerChain
+        from oracle import decode_ops, int4
+
+        c = chain.cfg
+        if world == 1:
+            L = chain.host_weights(len(chain.layers) - 1)
+            n2_want, _ = decode_ops.residual_rmsnorm(out["attn"].cpu(), out["r1"].cpu(), L["w2"], c.eps)
+            _need(_ulps16(out["n2"].cpu(), n2_want) <= 1, "chain: second norm more than one ulp off")
+            ref = int4.w4a16_projection(out["n2"].cpu(), L["up_packed"], L["up_scales"], None, group_size=c.group).double()
+            got = out["up_all"].cpu().double()
+            _need(bool(((got - ref).abs() <= 0.002 + 0.002 * ref.abs()).all()), "chain: up+gate projection outside its gate")
+            ref = int4.w4a16_projection(out["n1"].cpu(), L["qkv_packed"], L["qkv_scales"], None, group_size=c.group).double()
+            got = out["qkv"].cpu().double()
+            _need(bool(((got - ref).abs() <= 0.002 + 0.002 * ref.abs()).all()), "chain: QKV projection outside its gate")
+        else:
+            whole = DecodeLayerChain(c, layers=len(chain.layers), rank=0, world=1, seed=0, dependent_launch=False)
+            ref = whole.run_layers()
+            torch.cuda.synchronize()
+            _need(_rel_l2(out["attn"].float(), ref["attn"].float()) <= 2e-3, f"chain rank {rank}: assembled rotated Q differs from the unsharded run")
+            _need(_rel_l2(out["up_all"].float(), ref["up_all"].float()) <= 2e-3, f"chain rank {rank}: assembled up+gate differs from the unsharded run")
+    return check
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except GateFailure as failure:
+        sys.stderr.write(f"GATE FAILED: {failure}\n")
+        sys.stderr.flush()
+        os._exit(2)

@@ -13,10 +13,12 @@ import pathlib
 LIB_PATH = pathlib.Path(__file__).resolve().parent / "libxdk_b200.so"
 
 XDK_F32, XDK_BF16, XDK_F16 = 0, 1, 2
+XDK_STRICT_FP32, XDK_DEPENDENT_LAUNCH = 1, 2  # flags of the *_v2 entry points
 
 _p = ctypes.c_void_p
 _i64 = ctypes.c_int64
 _int = ctypes.c_int
+_uint = ctypes.c_uint
 
 # name -> (restype, argtypes); one row per symbol declared in include/xdk_b200.h
 SIGNATURES = {
@@ -25,15 +27,42 @@ SIGNATURES = {
     "xdk_last_cuda_error": (_int, []),
     "xdk_device_supported": (_int, [_int]),
     "xdk_fault_flags": (ctypes.c_uint, []),
+    "xdk_noop": (_int, [_uint, _p]),
     "xdk_rmsnorm": (_int, [_p, _p, _p, _p, _p, _i64, _i64, ctypes.c_float, _int, _p]),
+    "xdk_rmsnorm_v2": (_int, [_p, _p, _p, _p, _p, _i64, _i64, ctypes.c_float, _int, _uint, _p]),
     "xdk_gemv_f32": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, ctypes.c_size_t, _p]),
+    "xdk_gemv_f32_v2": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, ctypes.c_size_t, _uint, _p]),
     "xdk_gemv_tc_plan": (_int, [_i64, _i64, _i64, _int, _p]),
     "xdk_gemv_scratch_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _int]),
     "xdk_gemv_f32_static_scratch": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _p]),
     "xdk_rope_kv_append": (_int, [_p] * 11 + [_i64] * 11 + [_int, _int, _int, _p]),
+    "xdk_rope_kv_append_v2": (_int, [_p] * 11 + [_i64] * 11 + [_int, _int, _int, _uint, _p]),
     "xdk_w4a16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _p]),
+    "xdk_w4a16_v2": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _uint, _p]),
+    "xdk_quantize_int4": (_int, [_p, _int, _i64, _i64, _int, _p, _p, _p, _p]),
+    "xdk_peer_fault_flags": (ctypes.c_uint, []),
+    "xdk_peer_alloc": (_int, [ctypes.c_size_t, _p]),
+    "xdk_peer_free": (_int, [_p]),
+    "xdk_peer_export": (_int, [_p, _p]),
+    "xdk_peer_open": (_int, [_p, _p]),
+    "xdk_peer_close": (_int, [_p]),
+    "xdk_peer_barrier": (_int, [_p, _int, _int, _int, _uint, _uint, _p]),
+    "xdk_gemv_f32_peer": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _int, _int, _p, ctypes.c_size_t, _uint, _p]),
+    "xdk_w4a16_peer": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _uint, _p]),
+    "xdk_rope_kv_append_peer": (_int, [_p] * 11 + [_i64] * 11 + [_int, _int, _int, _uint, _p]),
     "xdk_unshard_columns": (_int, [_p, _p, _i64, _i64, _i64, _int, _p]),
 }
+
+
+XDK_MAX_PEERS = 8
+XDK_PEER_FLAG_BYTES = 8192
+
+
+class PeerOutStruct(ctypes.Structure):
+    """``xdk_peer_out`` of include/xdk_b200.h."""
+
+    _fields_ = [("ptr", ctypes.c_void_p * XDK_MAX_PEERS), ("world", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("ld", ctypes.c_int64), ("col0", ctypes.c_int64)]
 
 
 class NativeLibraryError(RuntimeError):

@@ -17,8 +17,19 @@ heads split, rank r owning q heads [r*Hq/g, ...), kv heads [r*Hkv/g, ...) and
 the same fraction of the up+gate columns; its QKV shard is laid out
 [its Q heads | its K heads | its V heads], i.e. exactly what its RoPE/append
 launch consumes, so nothing is exchanged before the append and every rank keeps
-its own KV-cache shard.  The rotated Q shards and the up+gate shards are
-all-gathered over NCCL (rank-major) and re-laid row-major by a small kernel.
+its own KV-cache shard.  The rotated Q shards and the up+gate shards have to
+reach every rank; two ways are built:
+
+* ``exchange="peer"`` (default): the append kernel and the up+gate projection
+  store their shard into the right columns of the full-width matrix in EVERY
+  rank's peer-mapped arena from their epilogues (peer.py), and one flag barrier
+  per exchange point orders the readers.  No collective, no re-layout kernel.
+* ``exchange="nccl"``: all-gather over NCCL (rank-major) and a small kernel that
+  re-lays the result row-major -- kept as the comparison arm.
+
+``dependent_launch=True`` launches every kernel of the chain as a programmatic
+dependent of its predecessor, so that scheduling, set-up and (for the
+projections) the first weight tiles overlap the predecessor's tail.
 """
 
 from __future__ import annotations
@@ -106,10 +117,13 @@ class DecodeLayerChain:
     """Weights, caches and index tensors of ``layers`` identical-shape layers for one rank."""
 
     def __init__(self, cfg: ChainConfig = ChainConfig(), *, layers: int = 1, rank: int = 0, world: int = 1,
-                 seed: int = 0, device="cuda", group=None):
+                 seed: int = 0, device="cuda", group=None, exchange: str = "peer", dependent_launch: bool = False):
         if cfg.q_heads % world or cfg.kv_heads % world or (2 * cfg.mlp) % world:
             raise ValueError("heads and MLP columns must divide by the number of ranks")
+        if exchange not in ("peer", "nccl"):
+            raise ValueError("exchange must be 'peer' or 'nccl'")
         self.cfg, self.rank, self.world, self.pg = cfg, rank, world, group
+        self.exchange, self.dependent = exchange, bool(dependent_launch)
         self.device = torch.device(device)
         c = cfg
         # Weights are drawn on the device (Philox, same values on every rank for one seed): drawing
@@ -149,12 +163,26 @@ class DecodeLayerChain:
         shape = (pages, c.page_size, hkv, d)
         self.k_cache = torch.full(shape, -999.0, dtype=torch.float16, device=self.device)
         self.v_cache = torch.full(shape, -999.0, dtype=torch.float16, device=self.device)
-        if world > 1:
+        self.arena = None
+        if world > 1 and exchange == "peer":
+            from .peer import PeerArena
+
+            # two copies of each full-width matrix, used by alternate layers: a rank that runs ahead into the
+            # next layer never stores into a matrix a slower rank is still reading
+            nbytes = 2 * (c.tokens * c.hidden + c.tokens * 2 * c.mlp) * 2 + 4096
+            self.arena = PeerArena(nbytes, group=group, device=self.device)
+            self.q_peer = [self.arena.matrix(c.tokens, c.hidden, torch.float16) for _ in range(2)]
+            self.up_peer = [self.arena.matrix(c.tokens, 2 * c.mlp, torch.float16) for _ in range(2)]
+            self.site_q, self.site_up = self.arena.new_site(), self.arena.new_site()
+            self.launches_per_layer = 7  # five kernels + two flag barriers
+        elif world > 1:
             self.q_gather = torch.empty(world, c.tokens, hq * d, dtype=torch.float16, device=self.device)
             self.up_gather = torch.empty(world, c.tokens, 2 * c.mlp // world, dtype=torch.float16, device=self.device)
-        self.q_full = torch.empty(c.tokens, c.hidden, dtype=torch.float16, device=self.device)
-        self.up_full = torch.empty(c.tokens, 2 * c.mlp, dtype=torch.float16, device=self.device)
-        self.launches_per_layer = 5 if world == 1 else 7
+            self.q_full = torch.empty(c.tokens, c.hidden, dtype=torch.float16, device=self.device)
+            self.up_full = torch.empty(c.tokens, 2 * c.mlp, dtype=torch.float16, device=self.device)
+            self.launches_per_layer = 7  # five kernels + two re-layout kernels (+ two NCCL all-gathers)
+        else:
+            self.launches_per_layer = 5
 
     def host_weights(self, layer: int = 0) -> dict:
         """CPU copies of one layer's unsharded weights (single-rank chains only; for checkers)."""
@@ -166,28 +194,43 @@ class DecodeLayerChain:
 
         c, L, dv = self.cfg, self.layers[layer], self.dev
         d, hq, hkv = c.head_dim, self.local_q_heads, self.local_kv_heads
+        dep = self.dependent
+        peer = self.arena is not None
         h = dv["h"] if h is None else h
         res = dv["res"] if res is None else res
-        n1, r1 = fused_residual_rmsnorm(h, res, L["w1"], c.eps)
-        qkv = w4a16_linear(n1, L["qkv_packed"], L["qkv_scales"], None, group_size=c.group)
+        n1, r1 = fused_residual_rmsnorm(h, res, L["w1"], c.eps, dependent_launch=dep)
+        qkv = w4a16_linear(n1, L["qkv_packed"], L["qkv_scales"], None, group_size=c.group, dependent_launch=dep)
         q = qkv[:, : hq * d].view(c.tokens, hq, d)
         k = qkv[:, hq * d: (hq + hkv) * d].view(c.tokens, hkv, d)
         v = qkv[:, (hq + hkv) * d:].view(c.tokens, hkv, d)
+        q_dst = self.q_peer[layer % 2] if peer else None
         q_rot = rope_gqa_paged_kv_append(q, k, v, dv["cos"], dv["sin"], dv["positions"], dv["page_table"],
                                          dv["sequence_ids"], self.k_cache, self.v_cache, page_size=c.page_size,
-                                         rope_dim=d, interleaved=False, kv_layout="NHD")
-        if self.world > 1:
+                                         rope_dim=d, interleaved=False, kv_layout="NHD", dependent_launch=dep,
+                                         q_peer_out=q_dst.out_for(self.rank * hq * d) if peer else None)
+        if peer:
+            self.arena.barrier(self.site_q, dependent_launch=dep)
+            attn = q_dst.local
+        elif self.world > 1:
             dist.all_gather_into_tensor(self.q_gather, q_rot.view(c.tokens, hq * d), group=self.pg)
             attn = unshard_columns(self.q_gather, self.q_full)
         else:
             attn = q_rot.view(c.tokens, c.hidden)
-        n2, r2 = fused_residual_rmsnorm(attn, r1, L["w2"], c.eps)
-        up = w4a16_linear(n2, L["up_packed"], L["up_scales"], None, group_size=c.group)
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.up_gather, up, group=self.pg)
-            up_all = unshard_columns(self.up_gather, self.up_full)
+        n2, r2 = fused_residual_rmsnorm(attn, r1, L["w2"], c.eps, dependent_launch=dep)
+        if peer:
+            up_dst = self.up_peer[layer % 2]
+            w4a16_linear(n2, L["up_packed"], L["up_scales"], None, group_size=c.group, dependent_launch=dep,
+                         peer_out=up_dst.out_for(self.rank * (2 * c.mlp // self.world)))
+            self.arena.barrier(self.site_up, dependent_launch=dep)
+            up = up_dst.local[:, self.rank * (2 * c.mlp // self.world): (self.rank + 1) * (2 * c.mlp // self.world)]
+            up_all = up_dst.local
         else:
-            up_all = up
+            up = w4a16_linear(n2, L["up_packed"], L["up_scales"], None, group_size=c.group, dependent_launch=dep)
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.up_gather, up, group=self.pg)
+                up_all = unshard_columns(self.up_gather, self.up_full)
+            else:
+                up_all = up
         return dict(n1=n1, r1=r1, qkv=qkv, q_rot=q_rot, attn=attn, n2=n2, r2=r2, up=up, up_all=up_all)
 
     def run_layers(self):

@@ -4,6 +4,10 @@
 namespace xdk {
 
 static thread_local int g_last_cuda_error = 0;
+static thread_local unsigned g_call_flags = 0;
+
+unsigned call_flags() { return g_call_flags; }
+void set_call_flags(unsigned flags) { g_call_flags = flags; }
 
 int note_launch(cudaError_t err) {
   if (err == cudaSuccess) return XDK_OK;
@@ -68,9 +72,23 @@ int sm_count() {
   return cached[dev];
 }
 
+namespace {
+__global__ void noop_kernel() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+}  // namespace
+
 }  // namespace xdk
 
 extern "C" {
+
+int xdk_noop(unsigned flags, void* stream) {
+  if (flags & ~XDK_DEPENDENT_LAUNCH) return XDK_ERR_ARG;
+  if (int st = xdk::require_sm100()) return st;
+  return xdk::launch_opts(xdk::noop_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), 1u,
+                          (flags & XDK_DEPENDENT_LAUNCH) != 0);
+}
 
 const char* xdk_strerror(int status) {
   switch (status) {
@@ -88,8 +106,16 @@ int xdk_abi_version(void) { return XDK_ABI_VERSION; }
 int xdk_last_cuda_error(void) { return xdk::g_last_cuda_error; }
 
 unsigned xdk_fault_flags(void) {
-  return xdk::gemv_fault_word() | (xdk::w4a16_fault_word() << 8) | (xdk::gemv_tc_fault_word() << 16);
+  const unsigned words[3] = {xdk::gemv_fault_word(), xdk::w4a16_fault_word(), xdk::gemv_tc_fault_word()};
+  unsigned out = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (words[i] & 0x80000000u) out |= 0x80000000u;  // the word could not be read: never report "healthy"
+    out |= (words[i] & 0x7fu) << (8 * i);
+  }
+  return out;
 }
+
+unsigned xdk_peer_fault_flags(void) { return xdk::peer_fault_word(); }
 
 int xdk_device_supported(int device) {
   int count = 0;

@@ -34,20 +34,27 @@ unsigned w4a16_fault_word();
 
 // tcgen05 FP32 projection (gemv_tc.cu): whether it takes the shape, and its launch
 bool gemv_tc_eligible(const float* x, const float* w, int64_t m, int64_t k, int64_t n, bool nk);
-int launch_gemv_tc(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, bool nk, cudaStream_t stream);
 bool gemv_tc_plan(int64_t m, int64_t k, int64_t n, bool nk, int32_t out[5]);  // {CTAs, K split, ring depth, smem bytes, units}
+
+// Flags of the *_v2 entry point that is executing on this host thread (0 outside one).
+unsigned call_flags();
+void set_call_flags(unsigned flags);
+struct CallFlagsScope {  // sets the flags for the duration of one entry point
+  explicit CallFlagsScope(unsigned flags) { set_call_flags(flags); }
+  ~CallFlagsScope() { set_call_flags(0u); }
+};
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename... Args>
-inline int launch(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                  unsigned cluster_y, Args... args) {
+inline int launch_opts(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       unsigned cluster_y, bool dependent, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   unsigned n_attr = 0;
   if (cluster_y > 1) {
     attr[n_attr].id = cudaLaunchAttributeClusterDimension;
@@ -56,10 +63,53 @@ inline int launch(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, c
     attr[n_attr].val.clusterDim.z = 1;
     ++n_attr;
   }
+  if (dependent) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
   return note_launch(cudaLaunchKernelEx(&cfg, kernel, args...));
 }
+template <typename... Args>
+inline int launch(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                  unsigned cluster_y, Args... args) {
+  return launch_opts(kernel, grid, block, smem, stream, cluster_y, false, args...);
+}
+// For kernels that execute pdl_wait() before they touch anything the preceding kernel of the stream wrote:
+// launched as a programmatic dependent of that kernel when the executing entry point was given
+// XDK_DEPENDENT_LAUNCH, so their scheduling and set-up overlap its tail.
+template <typename... Args>
+inline int launch_dependent(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args... args) {
+  return launch_opts(kernel, grid, block, smem, stream, 1u, (call_flags() & XDK_DEPENDENT_LAUNCH) != 0, args...);
+}
+
+// ---- where a kernel's output matrix goes --------------------------------------------------------
+// Either the caller's own buffer (world == 1), or the same place in EVERY rank's full-width buffer: rank r of a
+// column-sharded projection owns columns [col0, col0 + n) of a [rows, ld] matrix and its epilogue stores each
+// value into all `world` copies with ordinary global stores (peer-mapped memory over NVLink).  No collective
+// and no re-layout kernel follows; one flag barrier (peer.cu) per exchange point orders readers after writers.
+struct PeerOut {
+  void* ptr[XDK_MAX_PEERS];
+  int world;
+  int64_t ld;    // elements between consecutive rows at the destination
+  int64_t col0;  // first destination column of this call's output columns
+};
+inline PeerOut single_out(void* y, int64_t ld) {
+  PeerOut o = {};
+  o.ptr[0] = y;
+  o.world = 1;
+  o.ld = ld;
+  o.col0 = 0;
+  return o;
+}
+// Copies and checks the caller's descriptor (NULL: `fallback` / `ld` as the only destination).
+int make_out(const xdk_peer_out* peers, void* fallback, int64_t ld, PeerOut* out);
+unsigned peer_fault_word();
+int launch_gemv_tc(const float* x, const float* w, const float* bias, const PeerOut& y, int m, int k, int n, bool nk,
+                   cudaStream_t stream);
 
 // ---- device side -----------------------------------------------------------------------------
 
@@ -96,6 +146,19 @@ __device__ __forceinline__ float ld_stream_f1(const float* p) {
 __device__ __forceinline__ void st_stream16(void* p, const U4& v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
+}
+
+// Programmatic dependent launch.  pdl_wait: returns once every kernel this one depends on has completed and its
+// writes are visible (at once when the launch was an ordinary one).  pdl_launch_dependents: the next kernel of the
+// stream, if it was launched as a programmatic dependent, may be scheduled from now on.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename T>
+__device__ __forceinline__ void peer_store(const PeerOut& o, int64_t row, int64_t col, T v) {
+  const int64_t at = row * o.ld + o.col0 + col;
+#pragma unroll 1
+  for (int p = 0; p < o.world; ++p) static_cast<T*>(o.ptr[p])[at] = v;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -203,6 +266,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, uint64
         : "memory");
     if (done) return true;
     if ((i & 15u) == 15u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) return false;
+    }
+  }
+}
+// The same bounded wait for roles that mostly wait: every probe lets the hardware park the thread for up to
+// `park_ns` (it resumes as soon as the phase completes), so a waiting warp does not take issue slots from the
+// warps that compute.
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, unsigned parity, unsigned park_ns = 1000u,
+                                                 uint64_t budget_ns = 20000000ull) {
+  const uint32_t addr = smem_u32(bar);
+  uint64_t t0 = 0;
+  for (unsigned i = 0;; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity), "r"(park_ns)
+        : "memory");
+    if (done) return true;
+    if ((i & 3u) == 3u) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > budget_ns) return false;

@@ -30,7 +30,7 @@ struct GemvArgs {
   const float* x;
   const float* w;
   const float* bias;
-  float* y;
+  PeerOut out;  // y: the caller's buffer, or the same place in every rank's buffer
   int m, k, n;
   int k_slice;  // K elements per split-K slice (multiple of 32)
 };
@@ -90,7 +90,7 @@ __device__ __forceinline__ void finish_strip(float* part, const GemvArgs& a, int
       if (r < m_valid && col0 + c < a.n) {
         float v = part[o];
         if (a.bias) v += a.bias[col0 + c];
-        a.y[static_cast<size_t>(row0 + r) * a.n + col0 + c] = v;
+        peer_store(a.out, row0 + r, col0 + c, v);
       }
     }
     return;
@@ -106,7 +106,7 @@ __device__ __forceinline__ void finish_strip(float* part, const GemvArgs& a, int
     for (int s = 0; s < splits; ++s) v += *cluster.map_shared_rank(part + o, s);
     if (r < m_valid && col0 + c < a.n) {
       if (a.bias) v += a.bias[col0 + c];
-      a.y[static_cast<size_t>(row0 + r) * a.n + col0 + c] = v;
+      peer_store(a.out, row0 + r, col0 + c, v);
     }
   }
   cluster.sync();  // nobody leaves while a peer may still read its shared memory
@@ -331,7 +331,7 @@ __device__ unsigned int g_gemv_fault;  // set when a bounded wait gives up
 
 struct TileArgs {
   const float* bias;
-  float* y;
+  PeerOut out;
   float* scratch;  // [ctas][2][MT][128]
   int m, k, n;
   int strips, k_tiles;  // column strips, K tiles per strip
@@ -490,7 +490,7 @@ gemv_stream_kernel(TileArgs a, const __grid_constant__ CUtensorMap wmap, const _
               spill[r * kTileN + (o % kTileN)] = v;
             } else if (r < a.m && col < a.n) {
               if (a.bias) v += a.bias[col];
-              a.y[static_cast<size_t>(r) * a.n + col] = v;
+              peer_store(a.out, r, col, v);
             }
           }
           consumer_sync();  // red is reused by the next round / strip
@@ -530,7 +530,7 @@ gemv_stream_finish_kernel(TileArgs a) {
     const int r = o / kTileN, col = strip * kTileN + (o - r * kTileN);
     if (r < a.m && col < a.n) {
       if (a.bias) v += a.bias[col];
-      a.y[static_cast<size_t>(r) * a.n + col] = v;
+      peer_store(a.out, r, col, v);
     }
   }
 }
@@ -571,10 +571,10 @@ int dispatch_mt(const GemvArgs& a, bool nk, int splits, bool wide, bool wvec, bo
 }
 
 template <int MT>
-int launch_tile_stream(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, bool nk,
+int launch_tile_stream(const float* x, const float* w, const float* bias, const PeerOut& out, int m, int k, int n, bool nk,
                        float* scratch, cudaStream_t stream) {
   TileArgs a;
-  a.bias = bias, a.y = y, a.scratch = scratch;
+  a.bias = bias, a.out = out, a.scratch = scratch;
   a.m = m, a.k = k, a.n = n;
   a.strips = (n + kTileN - 1) / kTileN;
   a.k_tiles = (k + kTileK - 1) / kTileK;
@@ -670,9 +670,10 @@ extern "C" int xdk_gemv_f32_static_scratch(const float* x, const float* w, const
   float* scratch = static_scratch_for_current_device(&st);
   if (!scratch) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return m > 8 ? launch_tile_stream<16>(x, w, bias, y, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
+  const PeerOut out = single_out(y, n);
+  return m > 8 ? launch_tile_stream<16>(x, w, bias, out, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
                                         scratch, s)
-               : launch_tile_stream<8>(x, w, bias, y, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
+               : launch_tile_stream<8>(x, w, bias, out, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
                                        scratch, s);
 }
 
@@ -701,17 +702,38 @@ extern "C" size_t xdk_gemv_scratch_bytes(int64_t m, int64_t k, int64_t n, int we
 
 extern "C" int xdk_gemv_f32(const float* x, const float* w, const float* bias, float* y, int64_t m, int64_t k,
                             int64_t n, int weight_is_nk, int split_k, void* scratch, size_t scratch_bytes, void* stream) {
+  // version 1 semantics: passing scratch asks for strict FP32 arithmetic
+  return xdk_gemv_f32_v2(x, w, bias, y, m, k, n, weight_is_nk, split_k, scratch, scratch_bytes, scratch ? XDK_STRICT_FP32 : 0u,
+                         stream);
+}
+
+extern "C" int xdk_gemv_f32_v2(const float* x, const float* w, const float* bias, float* y, int64_t m, int64_t k,
+                               int64_t n, int weight_is_nk, int split_k, void* scratch, size_t scratch_bytes,
+                               unsigned flags, void* stream) {
+  if (!y || n <= 0) return XDK_ERR_ARG;
+  xdk_peer_out one = {};
+  one.ptr[0] = y, one.world = 1, one.ld = n, one.col0 = 0;
+  return xdk_gemv_f32_peer(x, w, bias, &one, m, k, n, weight_is_nk, split_k, scratch, scratch_bytes, flags, stream);
+}
+
+extern "C" int xdk_gemv_f32_peer(const float* x, const float* w, const float* bias, const xdk_peer_out* y_out, int64_t m,
+                                 int64_t k, int64_t n, int weight_is_nk, int split_k, void* scratch, size_t scratch_bytes,
+                                 unsigned flags, void* stream) {
   using namespace xdk;
-  if (!x || !w || !y) return XDK_ERR_ARG;
+  if (flags & ~(XDK_STRICT_FP32 | XDK_DEPENDENT_LAUNCH)) return XDK_ERR_ARG;
+  const bool strict = (flags & XDK_STRICT_FP32) != 0;
+  PeerOut y;
+  if (int st = make_out(y_out, nullptr, n, &y)) return st;
+  if (!x || !w) return XDK_ERR_ARG;
   if (m <= 0 || k <= 0 || n <= 0) return XDK_ERR_ARG;
   if (!(split_k == 0 || split_k == 1 || split_k == 2 || split_k == 4 || split_k == 8)) return XDK_ERR_ARG;
   if (m > 16 * 65535LL || k > 2147483647LL - 4096 || n > 2147483647LL - 4096) return XDK_ERR_LIMIT;
   if (int st = require_sm100()) return st;
   const bool nk = weight_is_nk != 0;
 
-  // 4 < M <= 16 without scratch: the tcgen05 kernel (split-TF32 products, FP32 accumulation; see gemv_tc.cu).
-  // A caller that passes scratch asks for strict FP32 FMA arithmetic and gets the tile-stream kernel below.
-  if (split_k == 0 && !scratch && gemv_tc_eligible(x, w, m, k, n, nk))
+  // 4 < M <= 16 unless strict FP32 was asked for: the tcgen05 kernel (split-TF32 products, FP32 accumulation; see
+  // gemv_tc.cu).  Everything below this line is FP32 FMA arithmetic.
+  if (split_k == 0 && !strict && gemv_tc_eligible(x, w, m, k, n, nk))
     return launch_gemv_tc(x, w, bias, y, static_cast<int>(m), static_cast<int>(k), static_cast<int>(n), nk,
                           static_cast<cudaStream_t>(stream));
 
@@ -737,7 +759,7 @@ extern "C" int xdk_gemv_f32(const float* x, const float* w, const float* bias, f
     // Smallest split that puts about 1.5 CTAs on every SM (2.7 for the light M <= 2 KN kernel), as long
     // as the whole grid is resident at once: a second wave costs more than any split gains.
     const int ctas_per_sm = mt <= 2 ? 4 : (mt <= 4 ? 3 : 2);  // register-limited residency of the MT variants
-    const int64_t slots = 148LL * ctas_per_sm;
+    const int64_t slots = static_cast<int64_t>(sm_count()) * ctas_per_sm;
     const int64_t want = (!nk && mt <= 2) ? 400 : 222;
     splits = 1;
     while (splits < 8 && strips_wide * splits < want && strips_wide * splits * 2 <= slots && k / (splits * 2) >= 256)
@@ -748,7 +770,7 @@ extern "C" int xdk_gemv_f32(const float* x, const float* w, const float* bias, f
   if (strips > 2147483647LL) return XDK_ERR_LIMIT;
 
   GemvArgs a;
-  a.x = x, a.w = w, a.bias = bias, a.y = y;
+  a.x = x, a.w = w, a.bias = bias, a.out = y;
   a.m = static_cast<int>(m), a.k = static_cast<int>(k), a.n = static_cast<int>(n);
   const int64_t per = (k + splits - 1) / splits;
   a.k_slice = static_cast<int>((per + 31) / 32 * 32);

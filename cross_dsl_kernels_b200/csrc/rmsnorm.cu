@@ -42,6 +42,8 @@ rmsnorm_row_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
                    T* __restrict__ y, T* __restrict__ residual_out, int nvec, float hidden_f, float eps) {
   constexpr int E = Elem<T>::kPerVec;
   __shared__ float scratch[THREADS / 32 + 1];
+  pdl_launch_dependents();
+  pdl_wait();  // x and residual may be the preceding kernel's output
   const size_t row_off = static_cast<size_t>(blockIdx.x) * nvec;  // in 16-byte vectors
   const U4* xv = reinterpret_cast<const U4*>(x) + row_off;
   const U4* rv = reinterpret_cast<const U4*>(residual) + row_off;
@@ -97,6 +99,8 @@ rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restrict__ residual, 
                        T* __restrict__ y, T* __restrict__ residual_out, int64_t hidden, float hidden_f,
                        float eps) {
   __shared__ float scratch[256 / 32 + 1];
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
   float sum_sq = 0.0f;
   for (int64_t i = threadIdx.x; i < hidden; i += 256) {
@@ -114,7 +118,7 @@ rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restrict__ residual, 
 template <typename T, int THREADS, int VPT>
 int launch_row(const void* x, const void* r, const void* w, void* y, void* ro, int64_t rows, int nvec,
                float hidden_f, float eps, cudaStream_t s) {
-  return launch(rmsnorm_row_kernel<T, THREADS, VPT>, dim3(static_cast<unsigned>(rows)), dim3(THREADS), 0, s, 1u,
+  return launch_dependent(rmsnorm_row_kernel<T, THREADS, VPT>, dim3(static_cast<unsigned>(rows)), dim3(THREADS), 0, s,
                 static_cast<const T*>(x), static_cast<const T*>(r), static_cast<const T*>(w), static_cast<T*>(y),
                 static_cast<T*>(ro), nvec, hidden_f, eps);
 }
@@ -141,7 +145,7 @@ int dispatch(const void* x, const void* r, const void* w, void* y, void* ro, int
     if constexpr (E == 4) XDK_ROW(512, 8);
 #undef XDK_ROW
   }
-  return launch(rmsnorm_generic_kernel<T>, dim3(static_cast<unsigned>(rows)), dim3(256), 0, s, 1u,
+  return launch_dependent(rmsnorm_generic_kernel<T>, dim3(static_cast<unsigned>(rows)), dim3(256), 0, s,
                 static_cast<const T*>(x), static_cast<const T*>(r), static_cast<const T*>(w), static_cast<T*>(y),
                 static_cast<T*>(ro), hidden, hidden_f, eps);
 }
@@ -151,6 +155,13 @@ int dispatch(const void* x, const void* r, const void* w, void* y, void* ro, int
 
 extern "C" int xdk_rmsnorm(const void* x, const void* residual, const void* weight, void* y, void* residual_out,
                            int64_t rows, int64_t hidden, float eps, int dtype, void* stream) {
+  return xdk_rmsnorm_v2(x, residual, weight, y, residual_out, rows, hidden, eps, dtype, 0u, stream);
+}
+
+extern "C" int xdk_rmsnorm_v2(const void* x, const void* residual, const void* weight, void* y, void* residual_out,
+                              int64_t rows, int64_t hidden, float eps, int dtype, unsigned flags, void* stream) {
+  if (flags & ~XDK_DEPENDENT_LAUNCH) return XDK_ERR_ARG;
+  xdk::CallFlagsScope scope(flags);
   if (!x || !residual || !weight || !y || !residual_out) return XDK_ERR_ARG;
   if (rows <= 0 || hidden <= 0 || !(eps > 0.0f) || !(eps < INFINITY)) return XDK_ERR_ARG;
   if (rows > 2147483647LL) return XDK_ERR_LIMIT;

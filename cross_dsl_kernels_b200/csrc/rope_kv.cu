@@ -41,6 +41,7 @@ struct RopeShape {
   int64_t max_pages;
   int64_t q_stride, k_stride, v_stride;  // elements between consecutive tokens of q, k, v
   int hnd;
+  PeerOut qout;  // rotated Q: row = token, column = head * head_dim + dim (plus col0), in every destination
 };
 
 // Element offset of (page, offset, head, dim 0) in a contiguous cache; identical integers to the
@@ -57,6 +58,8 @@ rope_append_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
                    const int64_t* __restrict__ positions, const int64_t* __restrict__ page_table,
                    const int64_t* __restrict__ sequence_ids, T* __restrict__ q_out, T* __restrict__ k_cache,
                    T* __restrict__ v_cache, RopeShape s, int units_rot_head, int units_token) {
+  pdl_launch_dependents();
+  pdl_wait();  // q, k, v may be the preceding kernel's output; the caches may still be read by it
   const int token = blockIdx.x;
   const int unit = blockIdx.y * 128 + threadIdx.x;
   if (unit >= units_token) return;
@@ -102,7 +105,7 @@ rope_append_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
 
   // ---- dependent index chain
   const int64_t pos = __ldg(positions + token);
-  int64_t dst_row = (static_cast<int64_t>(token) * s.q_heads + head) * s.head_dim;  // Q: contiguous q_out
+  int64_t dst_row = static_cast<int64_t>(token) * s.qout.ld + s.qout.col0 + static_cast<int64_t>(head) * s.head_dim;
   T* dst = q_out;
   if (kind != 0) {
     const int64_t seq = __ldg(sequence_ids + token);
@@ -139,6 +142,14 @@ rope_append_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
   }
   a.store(dst + dst_row + static_cast<int64_t>(first) * W);
   if (second >= 0) b.store(dst + dst_row + static_cast<int64_t>(second) * W);
+  if (kind == 0) {  // the other ranks' copies of the rotated Q
+#pragma unroll 1
+    for (int p = 1; p < s.qout.world; ++p) {
+      T* peer = static_cast<T*>(s.qout.ptr[p]);
+      a.store(peer + dst_row + static_cast<int64_t>(first) * W);
+      if (second >= 0) b.store(peer + dst_row + static_cast<int64_t>(second) * W);
+    }
+  }
 }
 
 template <typename T, int W, bool INTERLEAVED>
@@ -152,7 +163,7 @@ int launch_rope(const void* q, const void* k, const void* v, const float* cos, c
   if (units_token64 > 65535LL * 128) return XDK_ERR_LIMIT;
   const int units_token = static_cast<int>(units_token64);
   dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>((units_token + 127) / 128));
-  return launch(rope_append_kernel<T, W, INTERLEAVED>, grid, dim3(128), 0, stream, 1u, static_cast<const T*>(q),
+  return launch_dependent(rope_append_kernel<T, W, INTERLEAVED>, grid, dim3(128), 0, stream, static_cast<const T*>(q),
                 static_cast<const T*>(k), static_cast<const T*>(v), cos, sin, positions, page_table, sequence_ids,
                 static_cast<T*>(q_out), static_cast<T*>(k_cache), static_cast<T*>(v_cache), s, units_rot_head,
                 units_token);
@@ -167,6 +178,8 @@ rope_append_scalar_interleaved_kernel(const T* __restrict__ q, const T* __restri
                                       const int64_t* __restrict__ sequence_ids, T* __restrict__ q_out,
                                       T* __restrict__ k_cache, T* __restrict__ v_cache, RopeShape s,
                                       int units_rot_head, int units_token) {
+  pdl_launch_dependents();
+  pdl_wait();  // q, k, v may be the preceding kernel's output; the caches may still be read by it
   const int token = blockIdx.x;
   const int unit = blockIdx.y * 128 + threadIdx.x;
   if (unit >= units_token) return;
@@ -196,7 +209,7 @@ rope_append_scalar_interleaved_kernel(const T* __restrict__ q, const T* __restri
   float lo = Elem<T>::to_f32(src[src_row + d0]);
   float hi = d1 >= 0 ? Elem<T>::to_f32(src[src_row + d1]) : 0.0f;
   const int64_t pos = __ldg(positions + token);
-  int64_t dst_row = (static_cast<int64_t>(token) * s.q_heads + head) * s.head_dim;
+  int64_t dst_row = static_cast<int64_t>(token) * s.qout.ld + s.qout.col0 + static_cast<int64_t>(head) * s.head_dim;
   T* dst = q_out;
   if (kind != 0) {
     const int64_t seq = __ldg(sequence_ids + token);
@@ -212,8 +225,15 @@ rope_append_scalar_interleaved_kernel(const T* __restrict__ q, const T* __restri
     const float new_hi = __fadd_rn(__fmul_rn(lo, sn), __fmul_rn(hi, c));
     dst[dst_row + d0] = Elem<T>::from_f32(new_lo);
     dst[dst_row + d1] = Elem<T>::from_f32(new_hi);
+    if (kind == 0)
+      for (int p = 1; p < s.qout.world; ++p) {
+        static_cast<T*>(s.qout.ptr[p])[dst_row + d0] = Elem<T>::from_f32(new_lo);
+        static_cast<T*>(s.qout.ptr[p])[dst_row + d1] = Elem<T>::from_f32(new_hi);
+      }
   } else {
     dst[dst_row + d0] = Elem<T>::from_f32(lo);
+    if (kind == 0)
+      for (int p = 1; p < s.qout.world; ++p) static_cast<T*>(s.qout.ptr[p])[dst_row + d0] = Elem<T>::from_f32(lo);
   }
 }
 
@@ -223,8 +243,9 @@ int dispatch_all(const void* q, const void* k, const void* v, const float* cos, 
                  void* k_cache, void* v_cache, int64_t tokens, const RopeShape& s, bool interleaved,
                  cudaStream_t stream) {
   constexpr int E = Elem<T>::kPerVec;
-  const bool aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(q_out) && aligned16(k_cache) &&
-                       aligned16(v_cache);
+  bool aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(k_cache) && aligned16(v_cache) &&
+                 s.qout.ld % E == 0 && s.qout.col0 % E == 0;
+  for (int p = 0; p < s.qout.world; ++p) aligned = aligned && aligned16(s.qout.ptr[p]);
   // Vector path: whole 16-byte chunks, and rotation partners that fall on chunk boundaries.
   const bool vec = aligned && s.head_dim % E == 0 && s.q_stride % E == 0 && s.k_stride % E == 0 &&
                    s.v_stride % E == 0 && (interleaved ? s.rope_dim % E == 0 : (s.rope_dim / 2) % E == 0);
@@ -242,7 +263,7 @@ int dispatch_all(const void* q, const void* k, const void* v, const float* cos, 
   if (units_token64 > 65535LL * 128) return XDK_ERR_LIMIT;
   const int units_token = static_cast<int>(units_token64);
   dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>((units_token + 127) / 128));
-  return launch(rope_append_scalar_interleaved_kernel<T>, grid, dim3(128), 0, stream, 1u, static_cast<const T*>(q),
+  return launch_dependent(rope_append_scalar_interleaved_kernel<T>, grid, dim3(128), 0, stream, static_cast<const T*>(q),
                 static_cast<const T*>(k), static_cast<const T*>(v), cos, sin, positions, page_table, sequence_ids,
                 static_cast<T*>(q_out), static_cast<T*>(k_cache), static_cast<T*>(v_cache), s, units_rot_head,
                 units_token);
@@ -258,6 +279,40 @@ extern "C" int xdk_rope_kv_append(const void* q, const void* k, const void* v, c
                                   int64_t page_size, int64_t rope_dim, int64_t q_token_stride, int64_t k_token_stride,
                                   int64_t v_token_stride, int interleaved, int cache_is_hnd, int dtype,
                                   void* stream) {
+  return xdk_rope_kv_append_v2(q, k, v, cos, sin, positions, page_table, sequence_ids, q_out, k_cache, v_cache, tokens,
+                               q_heads, kv_heads, head_dim, cos_width, max_pages_per_seq, page_size, rope_dim,
+                               q_token_stride, k_token_stride, v_token_stride, interleaved, cache_is_hnd, dtype, 0u, stream);
+}
+
+extern "C" int xdk_rope_kv_append_v2(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                                     const int64_t* positions, const int64_t* page_table, const int64_t* sequence_ids,
+                                     void* q_out, void* k_cache, void* v_cache, int64_t tokens, int64_t q_heads,
+                                     int64_t kv_heads, int64_t head_dim, int64_t cos_width, int64_t max_pages_per_seq,
+                                     int64_t page_size, int64_t rope_dim, int64_t q_token_stride, int64_t k_token_stride,
+                                     int64_t v_token_stride, int interleaved, int cache_is_hnd, int dtype,
+                                     unsigned flags, void* stream) {
+  if (!q_out || q_heads <= 0 || head_dim <= 0) return XDK_ERR_ARG;
+  xdk_peer_out one = {};
+  one.ptr[0] = q_out, one.world = 1, one.ld = q_heads * head_dim, one.col0 = 0;
+  return xdk_rope_kv_append_peer(q, k, v, cos, sin, positions, page_table, sequence_ids, &one, k_cache, v_cache, tokens,
+                                 q_heads, kv_heads, head_dim, cos_width, max_pages_per_seq, page_size, rope_dim,
+                                 q_token_stride, k_token_stride, v_token_stride, interleaved, cache_is_hnd, dtype, flags,
+                                 stream);
+}
+
+extern "C" int xdk_rope_kv_append_peer(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                                       const int64_t* positions, const int64_t* page_table, const int64_t* sequence_ids,
+                                       const xdk_peer_out* q_dst, void* k_cache, void* v_cache, int64_t tokens,
+                                       int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t cos_width,
+                                       int64_t max_pages_per_seq, int64_t page_size, int64_t rope_dim,
+                                       int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
+                                       int interleaved, int cache_is_hnd, int dtype, unsigned flags, void* stream) {
+  if (flags & ~XDK_DEPENDENT_LAUNCH) return XDK_ERR_ARG;
+  xdk::CallFlagsScope scope(flags);
+  xdk::PeerOut qout;
+  if (int st = xdk::make_out(q_dst, nullptr, 1, &qout)) return st;
+  if (q_heads > 0 && head_dim > 0 && qout.ld < qout.col0 + q_heads * head_dim) return XDK_ERR_ARG;
+  void* q_out = qout.ptr[0];
   if (!q || !k || !v || !cos || !sin || !positions || !page_table || !sequence_ids || !q_out || !k_cache || !v_cache)
     return XDK_ERR_ARG;
   if (tokens <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || page_size <= 0 || max_pages_per_seq <= 0)
@@ -282,6 +337,7 @@ extern "C" int xdk_rope_kv_append(const void* q, const void* k, const void* v, c
   s.max_pages = max_pages_per_seq;
   s.q_stride = q_token_stride, s.k_stride = k_token_stride, s.v_stride = v_token_stride;
   s.hnd = cache_is_hnd ? 1 : 0;
+  s.qout = qout;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool il = interleaved != 0;
   switch (dtype) {

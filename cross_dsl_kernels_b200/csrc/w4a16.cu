@@ -8,7 +8,7 @@
 // FP16 rounding -- bit-identical to the format's definition half(float(q) * float(scale)), since
 // that FP32 product is exact.  Products with x accumulate in FP32.
 //
-// Two compute paths share the unpack:
+// Compute paths (they share the unpack):
 //   * M <= 2: SIMT.  Lanes stride over the packed row, weights feed mixed-precision FMAs
 //     (FP16 operands, FP32 accumulator) and a warp shuffle finishes each column.
 //   * 3 <= M <= 16: tensor cores.  The op is then a real [16 x K] x [K x N] contraction: x is padded to
@@ -38,6 +38,7 @@ struct W4Args {
   const __half* scales;
   const __half* bias;
   __half* y;
+  PeerOut out;        // where y goes for the tcgen05 kernel: y itself, or the same place in every rank's buffer
   int m, k, n;
   int group, groups;  // group size and scales per row
   int col_groups, groups_per_cta;
@@ -66,6 +67,39 @@ __device__ __forceinline__ void dequant8(uint32_t word, __half2 scale2, __half2 
   w[2] = __hmul2(q2, scale2);
   w[3] = __hmul2(q3, scale2);
 }
+
+// The same four half2, bit for bit, in fewer instructions when scale * 2^20 is finite (scale < 2^-4): a code masked
+// into bits 4..7 of a 16-bit lane with a zero exponent field IS the FP16 subnormal code * 2^-20, so one packed FMA
+// gives fma(code * 2^-20, scale * 2^20, -8 * scale) = round((code - 8) * scale) with a single rounding -- the
+// product and the addend are exact.  One byte permute, two multiplies by 16 (FMA pipe), four masks, four FMAs.
+__device__ __forceinline__ void dequant8_fma(uint32_t word, __half2 s20, __half2 m8s, __half2 (&w)[4]) {
+  constexpr uint32_t kMask = 0x00f000f0u;
+  const uint32_t sw = __byte_perm(word, 0, 0x2301);  // bytes (1,0,3,2): codes 2,3 / 6,7 into the low byte of each lane
+  uint32_t w16, s16;
+  asm("mul.lo.u32 %0, %1, 16;" : "=r"(w16) : "r"(word));
+  asm("mul.lo.u32 %0, %1, 16;" : "=r"(s16) : "r"(sw));
+  const uint32_t a0 = w16 & kMask, a1 = word & kMask, a2 = s16 & kMask, a3 = sw & kMask;
+  w[0] = __hfma2(*reinterpret_cast<const __half2*>(&a0), s20, m8s);
+  w[1] = __hfma2(*reinterpret_cast<const __half2*>(&a1), s20, m8s);
+  w[2] = __hfma2(*reinterpret_cast<const __half2*>(&a2), s20, m8s);
+  w[3] = __hfma2(*reinterpret_cast<const __half2*>(&a3), s20, m8s);
+}
+// A scale prepared for either path: `fast` when scale * 2^20 is finite.
+struct PreparedScale {
+  __half2 s2, s20, m8s;
+  bool fast;
+  __device__ __forceinline__ void set(__half scale) {
+    const __half big = __hmul(__hmul(scale, __float2half(1024.0f)), __float2half(1024.0f));  // exact, or inf
+    fast = (__half_as_ushort(big) & 0x7fffu) < 0x7c00u;
+    s2 = __half2half2(scale);
+    s20 = __half2half2(big);
+    m8s = __half2half2(__hmul(scale, __float2half(-8.0f)));
+  }
+  __device__ __forceinline__ void dequant(uint32_t word, __half2 (&w)[4]) const {
+    if (fast) dequant8_fma(word, s20, m8s, w);
+    else dequant8(word, s2, w);
+  }
+};
 
 // acc += a * b with FP16 operands and an FP32 accumulator in one instruction (sm_100 mixed FMA).
 __device__ __forceinline__ void fma_h(float& acc, __half a, __half b) {
@@ -441,12 +475,7 @@ w4a16_stream_kernel(W4Args a, StreamPlan plan, const __grid_constant__ CUtensorM
 
 template <int MR>
 int launch_stream(const W4Args& a, cudaStream_t stream) {
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      sm_count = 148;
-  }
+  const int sms = xdk::sm_count();
   StreamPlan plan;
   plan.total_blocks = (a.n + 7) / 8;
   plan.chunks = (a.k + kChunkK - 1) / kChunkK;
@@ -490,9 +519,9 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
       const int sz = 1 << s_log2;
       int n = 0;
       if (sz == 1) {
-        n = sm_count;
+        n = sms;
       } else {
-        cfg.gridDim = dim3(sm_count / sz * sz);
+        cfg.gridDim = dim3(sms / sz * sz);
         attr[0].val.clusterDim.x = sz;
         cfg.numAttrs = 1;
         if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
@@ -512,7 +541,7 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
     const int sz = 1 << s_log2;
     if (sz > plan.chunks) continue;
     const int fit = resident_clusters(s_log2);
-    if (fit * sz * 100 < sm_count * 94) continue;
+    if (fit * sz * 100 < sms * 94) continue;
     const int clusters = min(fit, plan.total_blocks);
     if ((plan.total_blocks + clusters - 1) / clusters > kStreamWarps * kMaxNB) continue;
     best_log2 = s_log2;
@@ -520,7 +549,7 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
   }
   plan.splits = 1 << best_log2;
   plan.clusters = min(resident_clusters(best_log2), plan.total_blocks);
-  if (plan.clusters <= 0) plan.clusters = min(sm_count, plan.total_blocks), plan.splits = 1;
+  if (plan.clusters <= 0) plan.clusters = min(sms, plan.total_blocks), plan.splits = 1;
   cfg.gridDim = dim3(plan.clusters * plan.splits);
   attr[0].val.clusterDim.x = plan.splits;
   cfg.numAttrs = plan.splits > 1 ? 1 : 0;
@@ -615,6 +644,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
   cur.init(blockIdx.x, plan.ctas, plan.total_units, a.k, kUStepK);
 
   if (threadIdx.x == 0) {
+    pdl_launch_dependents();  // the next kernel of the stream may be scheduled (it waits for this one's data itself)
     for (int i = 0; i < kUPackedBufs; ++i) {
       mbar_init(pk_full + i, 1);
       mbar_init(pk_empty + i, 8);   // one arrival per unpack warp
@@ -721,6 +751,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       }
       if (!ahead.next_step()) ahead_live = ahead.begin_strip();
     };
+    if (t == 0) pdl_wait();  // x is the preceding kernel's output; packed codes and scales (issued already) are not
     for (int i = 0; i < kUXBufs; ++i) issue();
     // A quarter warp moves an 8-row x 8-k-group block per pass along its diagonals: lane i takes k group i of row
     // (i + r) & 7, so the eight 16-byte loads (row pitch 512 B) and the eight stores (k-group pitch 128 B) each hit
@@ -763,7 +794,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
     const int c = lq * 32 + lane;             // this thread's TMEM lane
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(lq * 32) << 16);
     const uint32_t a_lane_base = lane_base + kUTmemA + kh * (kUStageCols / 2);
-    const __half* sc_row = reinterpret_cast<const __half*>(scbuf + c * scale_row_bytes);
+    const unsigned char* sc_row = scbuf + c * scale_row_bytes;  // groups % 8 == 0: 16-byte aligned, whole 16-byte blocks
     int strip_i = 0;
     bool ok = true;
     while (cur.begin_strip()) {
@@ -774,6 +805,8 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       const int k_range0 = ks * cur.kper;
       const int split = cur.split;
       if (ok) ok = mbar_wait(sc_full, strip_i & 1);
+      U4 sc8 = U4{0u, 0u, 0u, 0u};  // scales of groups [8 sc_blk, 8 sc_blk + 8) of this column
+      int sc_blk = -1;
       do {
         const int buf = cur.q % kUPackedBufs, s = cur.q % kUStages;
         if (ok) ok = mbar_wait(pk_full + buf, (cur.q / kUPackedBufs) & 1);
@@ -784,10 +817,20 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
           // lanes of a warp, which read the same piece of 32 different rows, spread over all bank groups
           const unsigned char* row = packed + buf * kUPackedBytes + c * (kUStepK / 2);
           const int k_half = k_range0 + cur.kc * kUStepK + kh * (kUStepK / 2);
+          PreparedScale ps;
 #pragma unroll
           for (int pc = 0; pc < kUStepK / 64; ++pc) {
-            // two pieces = 64 k lie inside one group (group >= 64)
-            const __half2 s2 = __half2half2(sc_row[(k_half + (pc & ~1) * 32) >> scale_shift]);
+            if ((pc & 1) == 0) {
+              // two pieces = 64 k lie inside one group (group >= 64).  The scales of 8 consecutive groups come with
+              // one 16-byte shared load (a per-scale read of this [lane][groups] array is a 16-way bank conflict).
+              const int g = (k_half + pc * 32) >> scale_shift;
+              if ((g >> 3) != sc_blk) {
+                sc_blk = g >> 3;
+                sc8 = *reinterpret_cast<const U4*>(sc_row + sc_blk * 16);
+              }
+              const uint32_t w2 = (g & 4) ? ((g & 2) ? sc8.w : sc8.z) : ((g & 2) ? sc8.y : sc8.x);
+              ps.set(__ushort_as_half(static_cast<unsigned short>((g & 1) ? (w2 >> 16) : (w2 & 0xffffu))));
+            }
             const int piece = kh * (kUStepK / 64) + pc;
             const U4 wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));  // rows past N are zero-filled: harmless
             uint32_t r[16];
@@ -795,7 +838,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
             for (int w = 0; w < 4; ++w) {
               const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
               __half2 h[4];
-              dequant8(word, s2, h);
+              ps.dequant(word, h);
 #pragma unroll
               for (int i = 0; i < 4; ++i) r[4 * w + i] = *reinterpret_cast<uint32_t*>(&h[i]);
             }
@@ -843,7 +886,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
         const float bv = a.bias ? __half2float(a.bias[col]) : 0.0f;
 #pragma unroll
         for (int m = 0; m < 16; ++m)
-          if (m < a.m) a.y[static_cast<size_t>(m) * a.n + col] = __float2half_rn(sum[m] + bv);
+          if (m < a.m) peer_store(a.out, m, col, __float2half_rn(sum[m] + bv));
       }
       // all 256 threads meet before the next strip's stages can reach the MMA warps (a_full needs all of them),
       // so the next strip's first MMAs cannot overwrite TMEM (nor its partials the shared buffer) while they are read
@@ -861,7 +904,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
   }
 }
 
-int launch_umma(const W4Args& a, cudaStream_t stream) {
+int launch_umma(const W4Args& a, bool dependent, cudaStream_t stream) {
   UmmaPlan plan;
   plan.total_units = (a.n + 31) / 32;
   plan.ctas = plan.total_units < sm_count() ? plan.total_units : sm_count();
@@ -886,7 +929,7 @@ int launch_umma(const W4Args& a, cudaStream_t stream) {
   }
   cudaError_t err = cudaFuncSetAttribute(w4a16_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return note_launch(err);
-  return launch(w4a16_umma_kernel, dim3(plan.ctas), dim3(kUThreads), smem, stream, 1u, a, plan, wmap, smap, xmap);
+  return launch_opts(w4a16_umma_kernel, dim3(plan.ctas), dim3(kUThreads), smem, stream, 1u, dependent, a, plan, wmap, smap, xmap);
 }
 
 // Any K (odd included), any alignment: warp per column, lane per byte (two codes), rows one at a
@@ -926,7 +969,7 @@ int launch_simt(W4Args a, cudaStream_t stream) {
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return note_launch(err);
   a.col_groups = (a.n + kWarps * CW - 1) / (kWarps * CW);
-  const int max_ctas = 4 * 148;
+  const int max_ctas = 4 * sm_count();
   a.groups_per_cta = (a.col_groups + max_ctas - 1) / max_ctas;
   const int ctas = (a.col_groups + a.groups_per_cta - 1) / a.groups_per_cta;
   return launch(kernel, dim3(ctas), dim3(kThreads), smem, stream, 1u, a);
@@ -948,7 +991,26 @@ unsigned w4a16_fault_word() {
 
 extern "C" int xdk_w4a16(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
                          int64_t m, int64_t k, int64_t n, int group_size, void* stream) {
+  return xdk_w4a16_v2(x, packed, scales, bias, y, m, k, n, group_size, 0u, stream);
+}
+
+extern "C" int xdk_w4a16_v2(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
+                            int64_t m, int64_t k, int64_t n, int group_size, unsigned flags, void* stream) {
+  if (!y || n < 1) return XDK_ERR_ARG;
+  xdk_peer_out one = {};
+  one.ptr[0] = y, one.world = 1, one.ld = n, one.col0 = 0;
+  return xdk_w4a16_peer(x, packed, scales, bias, &one, m, k, n, group_size, flags, stream);
+}
+
+extern "C" int xdk_w4a16_peer(const void* x, const uint8_t* packed, const void* scales, const void* bias,
+                              const xdk_peer_out* y_out, int64_t m, int64_t k, int64_t n, int group_size, unsigned flags,
+                              void* stream) {
   using namespace xdk;
+  if (flags & ~XDK_DEPENDENT_LAUNCH) return XDK_ERR_ARG;
+  PeerOut out;
+  if (int st = make_out(y_out, nullptr, n, &out)) return st;
+  void* y = out.ptr[0];
+  const bool plain = out.world == 1 && out.ld == n && out.col0 == 0;  // the kernels of this file write y[m][n] only
   if (!x || !packed || !scales || !y) return XDK_ERR_ARG;
   if (m < 1 || m > 16 || k < 1 || n < 1) return XDK_ERR_ARG;
   if (!(group_size == 32 || group_size == 64 || group_size == 128 || group_size == 256)) return XDK_ERR_ARG;
@@ -966,22 +1028,27 @@ extern "C" int xdk_w4a16(const void* x, const uint8_t* packed, const void* scale
   a.groups = static_cast<int>((k + group_size - 1) / group_size);
   a.col_groups = a.groups_per_cta = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool fast = k % 32 == 0 && aligned16(packed) && aligned16(x) && m * k * 2 <= 200 * 1024;
-  // M > 8 goes to the tcgen05 kernel (measured at K = 4096, M = 16 against the mma.sync kernel: 10.0 vs 12.5 us at
-  // N = 4096, 12.8 vs 15.9 at 6144, 17.5 vs 26.0 at 14336, 31.1 vs 42.4 at 28672).  XDK_W4A16_UMMA=0 sends it to the
-  // mma.sync kernel instead (kept for comparison runs and as the path for shapes the tcgen05 kernel does not take).
+  const bool dependent = (flags & XDK_DEPENDENT_LAUNCH) != 0;
+  a.out = out;
+  const bool vec_ok = k % 32 == 0 && aligned16(packed) && aligned16(x);  // 16-byte vectors of 32 codes
+  // M > 8, and every M whose output is strided or goes to several ranks: the tcgen05 kernel (measured at K = 4096,
+  // M = 16 against the mma.sync kernel: 10.0 vs 12.5 us at N = 4096, 12.8 vs 15.9 at 6144, 17.5 vs 26.0 at 14336,
+  // 31.1 vs 42.4 at 28672).  XDK_W4A16_UMMA=0 sends M > 8 to the mma.sync kernel instead (comparison runs).
   static const int umma_env = getenv("XDK_W4A16_UMMA") ? (getenv("XDK_W4A16_UMMA")[0] == '1' ? 1 : 0) : -1;
-  const bool umma_ok = fast && m > 8 && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales);
-  if (umma_env != 0 && umma_ok) {
-    const int st = launch_umma(a, s);
-    if (st != XDK_ERR_LIMIT) return st;
+  const bool umma_ok = vec_ok && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales);
+  if (umma_ok && ((umma_env != 0 && m > 8) || !plain)) {
+    const int st = launch_umma(a, dependent, s);
+    if (st != XDK_ERR_LIMIT || !plain) return st;
   }
-  if (fast && k % 128 == 0 && m >= 3) return m > 8 ? launch_stream<16>(a, s) : launch_stream<8>(a, s);
-  if (fast) {
-    if (m == 1) return launch_simt<1, 2>(a, s);
-    if (m == 2) return launch_simt<2, 2>(a, s);
-    if (m <= 4) return launch_simt<4, 2>(a, s);
-    if (m <= 8) return launch_simt<8, 1>(a, s);
+  if (!plain) return XDK_ERR_LIMIT;  // a strided or multi-rank destination needs the tcgen05 kernel's shape
+  if (vec_ok && k % 128 == 0 && m >= 3) return m > 8 ? launch_stream<16>(a, s) : launch_stream<8>(a, s);
+  // the SIMT kernel keeps all rows of x (padded to a power of two) in shared memory
+  const int mt = m == 1 ? 1 : (m == 2 ? 2 : (m <= 4 ? 4 : (m <= 8 ? 8 : 16)));
+  if (vec_ok && static_cast<int64_t>(mt) * k * 2 <= 200 * 1024) {
+    if (mt == 1) return launch_simt<1, 2>(a, s);
+    if (mt == 2) return launch_simt<2, 2>(a, s);
+    if (mt == 4) return launch_simt<4, 2>(a, s);
+    if (mt == 8) return launch_simt<8, 1>(a, s);
     return launch_simt<16, 1>(a, s);
   }
   return launch(w4a16_generic_kernel, dim3(static_cast<unsigned>((n + kWarps - 1) / kWarps)), dim3(kThreads), 0, s, 1u,

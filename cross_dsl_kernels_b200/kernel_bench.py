@@ -6,6 +6,16 @@ replayed and event-timed; ``gbps`` is the op's algorithmic bytes over the
 per-call median.  Used by bench.py and usable on its own:
 
     python -m cross_dsl_kernels_b200.kernel_bench [rmsnorm|gemv|rope|w4a16] ...
+
+Every ``bench_*`` function takes an optional ``check(stage, outputs)``: the
+caller's gate, run on the eager result, on a replay with poisoned outputs and
+on a replay after the inputs changed in place (timing.graph_median_us).  The
+functions hand the gate what it needs to recompute the expected result: call 0
+always runs on the seeded inputs of workloads.py, and the in-place change is
+"negate the activations".  ``dependent=True`` launches every call as a
+programmatic dependent of the call before it (rows named ``*_pdl``): the calls
+are independent of one another, so this shows what the op costs inside a chain
+whose kernels overlap their set-up with the predecessor's tail.
 """
 
 from __future__ import annotations
@@ -15,6 +25,7 @@ import sys
 
 import torch
 
+from . import _native
 from . import workloads as wl
 from .ops import decode_linear, fused_residual_rmsnorm, rope_gqa_paged_kv_append
 from .timing import graph_median_us, rotation_for
@@ -28,7 +39,7 @@ def _row(name: str, nbytes: int, timing: dict, sets: int, peak_gbps: float | Non
     gbps = nbytes / us * 1e-3
     row = {"kernel": name, "us": round(us, 3), "bytes": nbytes, "gbps": round(gbps, 1),
            "frac_of_8tbs": round(gbps / NOMINAL_HBM_GBPS, 4), "buffer_sets": sets,
-           "p10_us": round(timing["p10_us"], 3), "p90_us": round(timing["p90_us"], 3)}
+           "p10_us": round(timing["p10_us"], 3), "p90_us": round(timing["p90_us"], 3), "gated": timing["gated"]}
     if peak_gbps:
         row["frac_of_measured"] = round(gbps / peak_gbps, 4)
     row.update(extra)
@@ -39,33 +50,47 @@ def _calls_per_graph(sets: int) -> int:
     return sets * max(1, -(-20 // sets))  # at least 20 calls, whole rotations
 
 
-def bench_rmsnorm(rows: int, hidden: int, dtype, peak=None, replays=20) -> dict:
+def bench_noop(replays=20, dependent=False) -> dict:
+    """An empty kernel as a graph node: the floor under every per-call figure of this table."""
+    lib = _native.lib()
+    flags = _native.XDK_DEPENDENT_LAUNCH if dependent else 0
+
+    def call():
+        _native.check(lib.xdk_noop(flags, _native.stream_ptr(torch.device("cuda", torch.cuda.current_device()))), "xdk_noop")
+
+    t = graph_median_us([call] * 40, replays)
+    return {"kernel": "empty_kernel_graph_node" + ("_pdl" if dependent else ""), "us": round(t["median_us"], 3),
+            "p10_us": round(t["p10_us"], 3), "p90_us": round(t["p90_us"], 3), "bytes": 0, "gated": False}
+
+
+def bench_rmsnorm(rows: int, hidden: int, dtype, peak=None, replays=20, check=None, dependent=False) -> dict:
     nbytes = wl.rmsnorm_bytes(rows, hidden, dtype)
     sets = rotation_for(nbytes)
     x, r, w = (t.cuda() for t in wl.rmsnorm_inputs(rows, hidden, dtype))
     data = [(x.roll(s, 0), r.roll(s, 0), w) if s else (x, r, w) for s in range(sets)]
     n = _calls_per_graph(sets)
-    calls = [(lambda d=data[i % sets]: fused_residual_rmsnorm(d[0], d[1], d[2], 1e-6)) for i in range(n)]
-    t = graph_median_us(calls, replays)
-    name = f"rmsnorm_{str(dtype).split('.')[-1]}_{rows}x{hidden}"
+    calls = [(lambda d=data[i % sets]: fused_residual_rmsnorm(d[0], d[1], d[2], 1e-6, dependent_launch=dependent)) for i in range(n)]
+    t = graph_median_us(calls, replays, check=check, mutate=lambda: x.neg_())
+    name = f"rmsnorm_{str(dtype).split('.')[-1]}_{rows}x{hidden}" + ("_pdl" if dependent else "")
     return _row(name, nbytes, t, sets, peak)
 
 
 def bench_gemv(m: int, k: int, n: int, layout: str, split_k: int = 0, bias=True, peak=None, replays=20,
-               strict_fp32: bool = False) -> dict:
+               strict_fp32: bool = False, check=None, dependent=False) -> dict:
     nbytes = wl.projection_bytes(m, k, n, bias)
     sets = rotation_for(nbytes, cap=8)
     x, w, b = wl.projection_inputs(m, k, n, layout, bias)
     xd, bd = x.cuda(), (b.cuda() if bias else None)
     ws = [w.cuda()] + [torch.empty_like(w, device="cuda").normal_(0, k ** -0.5) for _ in range(sets - 1)]
     ncalls = _calls_per_graph(sets)
-    calls = [(lambda wt=ws[i % sets]: decode_linear(xd, wt, bd, weight_layout=layout, split_k=split_k, strict_fp32=strict_fp32)) for i in range(ncalls)]
-    t = graph_median_us(calls, replays)
-    name = f"gemv_f32_{layout}_m{m}_k{k}_n{n}_s{split_k}" + ("_strict" if strict_fp32 else "")
+    calls = [(lambda wt=ws[i % sets]: decode_linear(xd, wt, bd, weight_layout=layout, split_k=split_k, strict_fp32=strict_fp32,
+                                                    dependent_launch=dependent)) for i in range(ncalls)]
+    t = graph_median_us(calls, replays, check=check, mutate=lambda: xd.neg_())
+    name = (f"gemv_f32_{layout}_m{m}_k{k}_n{n}_s{split_k}" + ("_strict" if strict_fp32 else "") + ("_pdl" if dependent else ""))
     return _row(name, nbytes, t, sets, peak, split_k=split_k)
 
 
-def bench_rope(dtype, layout: str, rope_dim: int, peak=None, replays=20, **shape) -> dict:
+def bench_rope(dtype, layout: str, rope_dim: int, peak=None, replays=20, check=None, dependent=False, **shape) -> dict:
     case = wl.rope_inputs(rope_dim=rope_dim, layout=layout, dtype=dtype, **shape)
     tokens, hq, dim = case["q"].shape
     hkv = case["k"].shape[1]
@@ -74,16 +99,26 @@ def bench_rope(dtype, layout: str, rope_dim: int, peak=None, replays=20, **shape
     dev = {key: (val.cuda() if torch.is_tensor(val) else val) for key, val in case.items()}
     kc = torch.full(case["cache_shape"], -999.0, dtype=dtype, device="cuda")
     vc = torch.full_like(kc, -999.0)
-    qs = [dev["q"].roll(s, 0) for s in range(sets)]
-    calls = [(lambda q=qs[i % sets]: rope_gqa_paged_kv_append(
-        q, dev["k"], dev["v"], dev["cos"], dev["sin"], dev["positions"], dev["page_table"], dev["sequence_ids"], kc, vc,
-        page_size=case["page_size"], rope_dim=rope_dim, interleaved=False, kv_layout=layout)) for i in range(24)]
-    t = graph_median_us(calls, replays)
-    name = f"rope_kv_{str(dtype).split('.')[-1]}_{layout}_rd{rope_dim}_t{tokens}"
+    qs = [dev["q"]] + [dev["q"].roll(s, 0) for s in range(1, sets)]
+
+    def run(q):
+        q_out = rope_gqa_paged_kv_append(q, dev["k"], dev["v"], dev["cos"], dev["sin"], dev["positions"], dev["page_table"],
+                                         dev["sequence_ids"], kc, vc, page_size=case["page_size"], rope_dim=rope_dim,
+                                         interleaved=False, kv_layout=layout, dependent_launch=dependent)
+        return q_out, kc, vc  # the caches are outputs too (the gate checks the written slots and the sentinels)
+
+    calls = [(lambda q=qs[i % sets]: run(q)) for i in range(24)]
+
+    def mutate():
+        for key in ("q", "k", "v"):
+            dev[key].neg_()
+
+    t = graph_median_us(calls, replays, check=check, mutate=mutate)
+    name = f"rope_kv_{str(dtype).split('.')[-1]}_{layout}_rd{rope_dim}_t{tokens}" + ("_pdl" if dependent else "")
     return _row(name, nbytes, t, sets, peak)
 
 
-def bench_w4a16(m: int, k: int, n: int, group: int = 128, peak=None, replays=20) -> dict:
+def bench_w4a16(m: int, k: int, n: int, group: int = 128, peak=None, replays=20, check=None, dependent=False) -> dict:
     nbytes = wl.w4a16_bytes(m, k, n, group)
     sets = rotation_for(nbytes, cap=48)
     x, packed, scales, _ = wl.w4a16_inputs(m, k, n, group)
@@ -92,20 +127,28 @@ def bench_w4a16(m: int, k: int, n: int, group: int = 128, peak=None, replays=20)
     ss = [sd] + [sd.clone() for _ in range(sets - 1)]
     outs = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in range(sets)]
     ncalls = _calls_per_graph(sets)
-    calls = [(lambda i=i: w4a16_linear(xd, ps[i % sets], ss[i % sets], None, group_size=group, out=outs[i % sets])) for i in range(ncalls)]
-    t = graph_median_us(calls, replays)
-    return _row(f"w4a16_m{m}_k{k}_n{n}_g{group}", nbytes, t, sets, peak)
+    calls = [(lambda i=i: w4a16_linear(xd, ps[i % sets], ss[i % sets], None, group_size=group, out=outs[i % sets],
+                                       dependent_launch=dependent)) for i in range(ncalls)]
+    t = graph_median_us(calls, replays, check=check, mutate=lambda: xd.neg_())
+    return _row(f"w4a16_m{m}_k{k}_n{n}_g{group}" + ("_pdl" if dependent else ""), nbytes, t, sets, peak)
 
 
-def bench_chain(rank: int = 0, world: int = 1, layers: int = 4, peak=None, replays=20, group=None) -> dict:
+def bench_chain(rank: int = 0, world: int = 1, layers: int = 4, peak=None, replays=20, group=None, exchange: str = "peer",
+                dependent: bool = False, check=None) -> dict:
     """Decode-layer chain: ``layers`` layers with distinct weights (more than L2 in total) in one
-    CUDA graph; reports the per-layer median.  With world > 1 every rank must call this."""
+    CUDA graph; reports the per-layer median.  With world > 1 every rank must call this.
+    ``check(chain, outputs_of_last_layer)`` (optional) is run on the eager result before timing."""
     from .chain import ChainConfig, DecodeLayerChain
     from .timing import capture, replay_times_ms
     import statistics
 
     cfg = ChainConfig()
-    chain = DecodeLayerChain(cfg, layers=layers, rank=rank, world=world, group=group)
+    chain = DecodeLayerChain(cfg, layers=layers, rank=rank, world=world, group=group, exchange=exchange,
+                             dependent_launch=dependent)
+    if check is not None:
+        out = chain.run_layers()
+        torch.cuda.synchronize()
+        check(chain, out)
     graph = capture([chain.run_layers])
     times = replay_times_ms(graph, replays, 3)
     us = statistics.median(times) * 1e3 / layers
@@ -115,16 +158,25 @@ def bench_chain(rank: int = 0, world: int = 1, layers: int = 4, peak=None, repla
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
         us = float(t.item())
     nbytes = cfg.algorithmic_bytes()
-    row = {"kernel": f"decode_layer_chain_fp16_t{cfg.tokens}_h{cfg.hidden}_ctx{cfg.context}", "us": round(us, 3),
+    name = f"decode_layer_chain_fp16_t{cfg.tokens}_h{cfg.hidden}_ctx{cfg.context}" + ("_pdl" if dependent else "")
+    row = {"kernel": name, "us": round(us, 3),
            "bytes": nbytes, "gbps": round(nbytes / us * 1e-3, 1), "frac_of_8tbs": round(nbytes / us * 1e-3 / (NOMINAL_HBM_GBPS * world), 4),
-           "n_gpus": world, "layers_in_graph": layers, "launches_per_layer": chain.launches_per_layer}
+           "n_gpus": world, "layers_in_graph": layers, "launches_per_layer": chain.launches_per_layer,
+           "exchange": exchange if world > 1 else "none", "dependent_launch": dependent, "gated": check is not None}
     if peak:
         row["frac_of_measured"] = round(nbytes / us * 1e-3 / (peak * world), 4)
+    del graph
+    if chain.arena is not None:
+        torch.cuda.synchronize()
+        import torch.distributed as dist
+        dist.barrier(group=group)
+        chain.arena.close()
     return row
 
 
 def table(which=("rmsnorm", "gemv", "rope", "w4a16"), peak=None, split_sweep=True) -> list[dict]:
-    rows = []
+    """The ungated table (command-line use); bench.py builds the gated one row by row."""
+    rows = [bench_noop()]
     if "rmsnorm" in which:
         for dtype in (torch.float32, torch.bfloat16):
             for r in (256, 4096):

@@ -39,8 +39,16 @@ def _gate(t: torch.Tensor) -> None:
         raise ValueError("these kernels are built for sm_100a (B200) only")
 
 
-def fused_residual_rmsnorm(x, residual, weight, eps, *, return_residual: bool = True):
-    """(y, residual_out) = RMSNorm(x + residual) * weight and the FP32 sum rounded to dtype."""
+def _flags(dependent_launch: bool, strict_fp32: bool = False) -> int:
+    return (_native.XDK_DEPENDENT_LAUNCH if dependent_launch else 0) | (_native.XDK_STRICT_FP32 if strict_fp32 else 0)
+
+
+def fused_residual_rmsnorm(x, residual, weight, eps, *, return_residual: bool = True, dependent_launch: bool = False):
+    """(y, residual_out) = RMSNorm(x + residual) * weight and the FP32 sum rounded to dtype.
+
+    ``dependent_launch=True`` (every op of this module takes it) launches the kernel as a programmatic
+    dependent of the preceding kernel on the stream, so that its scheduling and set-up overlap that
+    kernel's tail; the caller promises that ``weight`` was not written by that kernel."""
     _gate(x)
     _need(residual.is_cuda and weight.is_cuda, "residual and weight must be CUDA tensors")
     _need(x.dtype in _RMS_DTYPES, "x must be float32, bfloat16 or float16")
@@ -57,21 +65,26 @@ def fused_residual_rmsnorm(x, residual, weight, eps, *, return_residual: bool = 
     with torch.cuda.device(x.device):
         y = torch.empty_like(x)
         residual_out = torch.empty_like(residual)
-        status = _native.lib().xdk_rmsnorm(
+        status = _native.lib().xdk_rmsnorm_v2(
             x.data_ptr(), residual.data_ptr(), weight.data_ptr(), y.data_ptr(), residual_out.data_ptr(),
-            x.shape[0], x.shape[1], eps, _native.dtype_code(x.dtype), _native.stream_ptr(x.device))
+            x.shape[0], x.shape[1], eps, _native.dtype_code(x.dtype), _flags(dependent_launch),
+            _native.stream_ptr(x.device))
     _native.check(status, "xdk_rmsnorm")
     return y, (residual_out if return_residual else None)
 
 
 def decode_linear(x, weight, bias=None, *, out_dtype=None, weight_layout: str = "KN", split_k: int = 0,
-                  strict_fp32: bool = False):
+                  strict_fp32: bool = False, dependent_launch: bool = False, peer_out=None):
     """y = x @ W (+ bias) in FP32.  ``split_k`` in {0 (auto), 1, 2, 4, 8}.
 
     With ``split_k=0`` and 4 < M <= 16 a large projection runs on the tensor cores as split-TF32
     products with FP32 accumulation (relative L2 error ~1e-6 against an FP64 product, inside the
     projection's 1e-5 gate).  ``strict_fp32=True`` keeps such shapes on the CUDA-core tile-stream
-    kernel, whose every product and sum is an FP32 FMA; it needs a scratch block per call."""
+    kernel, whose every product and sum is an FP32 FMA; it needs a scratch block per call.
+
+    ``peer_out`` (multi-GPU; from :meth:`cross_dsl_kernels_b200.peer.PeerMatrix.out_for`): the kernel stores its
+    [M, N] result into columns [col0, col0 + N) of the full-width matrix on every rank instead of allocating
+    an output; the call then returns None and the caller orders readers with ``PeerArena.barrier``."""
     _need(x.dim() == 2, "x must be a 2D tensor shaped [M, K]")
     _need(weight.dim() == 2, "weight must be a 2D tensor")
     _need(weight_layout in ("KN", "NK"), "weight_layout must be 'KN' or 'NK'")
@@ -94,21 +107,33 @@ def decode_linear(x, weight, bias=None, *, out_dtype=None, weight_layout: str = 
         _need(bias.is_contiguous(), "bias must be contiguous")
         bias_ptr = bias.data_ptr()
     with torch.cuda.device(x.device):
-        y = torch.empty((m, n), device=x.device, dtype=torch.float32)
         lib = _native.lib()
-        # Scratch selects the balanced tile-stream path (4 < M <= 16, split_k = 0).  A fresh block from
+        if peer_out is not None:
+            _need(peer_out.ld >= peer_out.col0 + n, "peer_out is narrower than col0 + N")
+            need = lib.xdk_gemv_scratch_bytes(m, k, n, int(nk)) if (split_k == 0 and strict_fp32) else 0
+            scratch = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
+            import ctypes
+            status = lib.xdk_gemv_f32_peer(x.data_ptr(), weight.data_ptr(), bias_ptr, ctypes.byref(peer_out), m, k, n,
+                                           int(nk), split_k, scratch.data_ptr() if need else None, need,
+                                           _flags(dependent_launch, strict_fp32), _native.stream_ptr(x.device))
+            _native.check(status, "xdk_gemv_f32_peer")
+            return None
+        y = torch.empty((m, n), device=x.device, dtype=torch.float32)
+        # Scratch lets strict-FP32 calls use the balanced tile-stream path (4 < M <= 16, split_k = 0).  A fresh block from
         # torch's caching allocator per call: stream-ordered, so overlapping calls never share it,
         # and under graph capture it lives in the graph's private pool.
         need = lib.xdk_gemv_scratch_bytes(m, k, n, int(nk)) if (split_k == 0 and strict_fp32) else 0
         scratch = torch.empty(need, device=x.device, dtype=torch.uint8) if need else None
-        status = lib.xdk_gemv_f32(x.data_ptr(), weight.data_ptr(), bias_ptr, y.data_ptr(), m, k, n, int(nk), split_k,
-                                  scratch.data_ptr() if need else None, need, _native.stream_ptr(x.device))
+        status = lib.xdk_gemv_f32_v2(x.data_ptr(), weight.data_ptr(), bias_ptr, y.data_ptr(), m, k, n, int(nk), split_k,
+                                     scratch.data_ptr() if need else None, need, _flags(dependent_launch, strict_fp32),
+                                     _native.stream_ptr(x.device))
     _native.check(status, "xdk_gemv_f32")
     return y
 
 
 def rope_gqa_paged_kv_append(q, k, v, cos, sin, positions, page_table, sequence_ids, k_cache, v_cache, *,
-                             page_size: int, rope_dim: int, interleaved: bool, kv_layout: str = "NHD"):
+                             page_size: int, rope_dim: int, interleaved: bool, kv_layout: str = "NHD",
+                             dependent_launch: bool = False, q_peer_out=None):
     """Rotate Q and K, write rotated K and V into the paged caches in place, return rotated Q.
 
     Index values are trusted: validate them once at set-up with
@@ -154,12 +179,20 @@ def rope_gqa_paged_kv_append(q, k, v, cos, sin, positions, page_table, sequence_
     _need(tuple(k_cache.shape[1:]) == want, f"{layout} cache dimensions must be (pages, {want})")
     validate_cache_storage((q, k, v, cos, sin, positions, page_table, sequence_ids), k_cache, v_cache)
     with torch.cuda.device(q.device):
-        q_out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-        status = _native.lib().xdk_rope_kv_append(
+        import ctypes
+        if q_peer_out is None:  # rotated Q into a fresh contiguous tensor
+            q_out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            dst = _native.PeerOutStruct()
+            dst.ptr[0], dst.world, dst.ld, dst.col0 = q_out.data_ptr(), 1, q_heads * head_dim, 0
+        else:  # multi-GPU: rotated Q into this rank's columns of the full-width matrix on every rank
+            q_out, dst = None, q_peer_out
+            _need(dst.ld >= dst.col0 + q_heads * head_dim, "q_peer_out is narrower than col0 + q_heads * head_dim")
+        status = _native.lib().xdk_rope_kv_append_peer(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(),
-            page_table.data_ptr(), sequence_ids.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            page_table.data_ptr(), sequence_ids.data_ptr(), ctypes.byref(dst), k_cache.data_ptr(), v_cache.data_ptr(),
             tokens, q_heads, kv_heads, head_dim, cos.shape[1], page_table.shape[1], page_size, rope_dim,
             q.stride(0) if tokens > 1 else q_heads * head_dim, k.stride(0) if tokens > 1 else kv_heads * head_dim,
-            v.stride(0) if tokens > 1 else kv_heads * head_dim, int(bool(interleaved)), int(layout == "HND"), _native.dtype_code(dtype), _native.stream_ptr(q.device))
+            v.stride(0) if tokens > 1 else kv_heads * head_dim, int(bool(interleaved)), int(layout == "HND"), _native.dtype_code(dtype), _flags(dependent_launch),
+            _native.stream_ptr(q.device))
     _native.check(status, "xdk_rope_kv_append")
     return q_out

@@ -87,6 +87,41 @@ def quantize_int4(weight: torch.Tensor, group_size: int = 128):
     return pack_int4(q.view(n, -1)[:, :k]), scale.contiguous()
 
 
+def quantize_int4_device(weight: torch.Tensor, group_size: int = 128):
+    """:func:`quantize_int4` for a weight matrix that already lives on a B200: one CUDA kernel, no FP32 copy of
+    the matrix, packed bytes and scales bit-identical to the host function.  Raises the same ValueErrors
+    (it reads a status word back, so it synchronises: a set-up step, like the host function)."""
+    from . import _native
+
+    _require_group(group_size)
+    if weight.ndim != 2 or weight.numel() == 0 or not weight.is_floating_point():
+        raise ValueError("weight must be a nonempty floating-point [N, K] matrix")
+    if weight.requires_grad:
+        raise ValueError("quantization is forward-only; detach weight explicitly")
+    if not weight.is_cuda:
+        raise ValueError("quantize_int4_device needs a CUDA tensor; use quantize_int4 on the host")
+    if weight.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        weight = weight.float()
+    weight = weight.contiguous()
+    n, k = weight.shape
+    with torch.cuda.device(weight.device):
+        packed = torch.empty((n, (k + 1) // 2), dtype=torch.uint8, device=weight.device)
+        scales = torch.empty((n, _groups(k, group_size)), dtype=torch.float16, device=weight.device)
+        status = torch.zeros(1, dtype=torch.int32, device=weight.device)
+        rc = _native.lib().xdk_quantize_int4(weight.data_ptr(), _native.dtype_code(weight.dtype), n, k, group_size,
+                                             packed.data_ptr(), scales.data_ptr(), status.data_ptr(),
+                                             _native.stream_ptr(weight.device))
+    _native.check(rc, "xdk_quantize_int4")
+    flags = int(status.item())
+    if flags & 1:
+        raise ValueError("weight must be finite")
+    if flags & 2:
+        raise ValueError("group scales cannot be represented in FP16")
+    if flags & 4:
+        raise ValueError("dequantized weights cannot be represented in FP16")
+    return packed, scales
+
+
 def dequantize_int4(packed: torch.Tensor, scales: torch.Tensor, k: int, group_size: int = 128) -> torch.Tensor:
     """FP16 [N, K] weights, each rounded once from the FP32 product q * scale."""
     _require_group(group_size)

@@ -26,7 +26,10 @@ def rotation_for(working_set_bytes: int, target_bytes: int = 3 * L2_BYTES, cap: 
     return max(1, min(cap, -(-target_bytes // max(1, working_set_bytes))))
 
 
-def capture(calls: Sequence[Callable[[], object]], stream: torch.cuda.Stream | None = None) -> torch.cuda.CUDAGraph:
+def capture(calls: Sequence[Callable[[], object]], stream: torch.cuda.Stream | None = None, outputs: list | None = None
+            ) -> torch.cuda.CUDAGraph:
+    """Warm the calls up, then capture them back to back into one graph.  ``outputs`` (optional list) receives
+    what each captured call returned: tensors in the graph's private pool that every replay rewrites."""
     stream = stream or torch.cuda.Stream()
     stream.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(stream):
@@ -36,7 +39,9 @@ def capture(calls: Sequence[Callable[[], object]], stream: torch.cuda.Stream | N
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=stream):
         for fn in calls:
-            fn()
+            out = fn()
+            if outputs is not None:
+                outputs.append(out)
     return graph
 
 
@@ -55,8 +60,44 @@ def replay_times_ms(graph: torch.cuda.CUDAGraph, replays: int = 20, warmup: int 
     return times
 
 
-def graph_median_us(calls: Sequence[Callable[[], object]], replays: int = 20, warmup: int = 3) -> dict:
-    graph = capture(calls)
+def _poison(obj) -> None:
+    if torch.is_tensor(obj):
+        if obj.is_floating_point():
+            obj.fill_(float("nan"))
+    elif isinstance(obj, (tuple, list)):
+        for item in obj:
+            _poison(item)
+
+
+def graph_median_us(calls: Sequence[Callable[[], object]], replays: int = 20, warmup: int = 3,
+                    check: Callable[[str, object], None] | None = None, mutate: Callable[[], None] | None = None) -> dict:
+    """Per-call median of a graph of back-to-back calls.
+
+    ``check(stage, output_of_call_0)`` (optional) is the gate, and it raises on a mismatch.  It runs three times:
+    ``"eager"`` on the first call's result before anything is timed; ``"poisoned"`` on the captured output of call 0
+    after a replay whose output buffers were filled with NaN first (a replay that silently does nothing fails);
+    ``"changed"`` after ``mutate()`` has changed the INPUT contents of call 0 in place at their fixed addresses and
+    the graph was replayed again (a graph that baked values in instead of addresses fails).  ``mutate`` is then
+    called a second time and must restore the inputs.  This is the discipline of upstream's
+    benchmarks/compare.py:28-41, 247-258 and benchmarks/gemv_cuda_benchmark.py:97-126."""
+    if check is not None:
+        first = calls[0]()
+        torch.cuda.synchronize()
+        check("eager", first)
+    outputs: list = []
+    graph = capture(calls, outputs=outputs)
+    if check is not None:
+        _poison(outputs)
+        graph.replay()
+        torch.cuda.synchronize()
+        check("poisoned", outputs[0])
+        if mutate is not None:
+            mutate()
+            _poison(outputs)
+            graph.replay()
+            torch.cuda.synchronize()
+            check("changed", outputs[0])
+            mutate()
     times = replay_times_ms(graph, replays, warmup)
     per_call = [t * 1e3 / len(calls) for t in times]
     ordered = sorted(per_call)
@@ -67,6 +108,7 @@ def graph_median_us(calls: Sequence[Callable[[], object]], replays: int = 20, wa
         "min_us": ordered[0],
         "calls_per_graph": len(calls),
         "replays": replays,
+        "gated": check is not None,
     }
 
 
@@ -94,7 +136,15 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device_index: int = 0, period_ms: int = 100):
-        self.cmd = ["nvidia-smi", f"--id={device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+        # nvidia-smi numbers GPUs by PCI order, CUDA by CUDA_VISIBLE_DEVICES: address the GPU by its UUID
+        # (a read-only query), falling back to the ordinal when the UUID cannot be had
+        ident = str(device_index)
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            ident = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            pass
+        self.cmd = ["nvidia-smi", f"--id={ident}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                     "-lms", str(period_ms)]
         self.rows: list[list[str]] = []
         self.proc = None

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define XDK_ABI_VERSION 1
+#define XDK_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define XDK_API __attribute__((visibility("default")))
@@ -46,6 +46,43 @@ typedef enum xdk_dtype {
   XDK_F16 = 2 /* extension: upstream's CUDA kernels take FP32/BF16 only */
 } xdk_dtype;
 
+/*
+ * Flags of the *_v2 entry points (ABI version 2).  Every *_v2 function takes the arguments of its
+ * version-1 namesake plus `unsigned flags` before the stream; the version-1 functions stay and behave
+ * as before.
+ *   XDK_STRICT_FP32       (xdk_gemv_f32_v2 only) every product and sum is an FP32 FMA on the CUDA cores;
+ *                         without it a large 4 < M <= 16 projection may run on the tensor cores as
+ *                         split-TF32 products (inside the projection's 1e-5 gate, not bit-identical).
+ *                         The choice of arithmetic never depends on whether scratch was passed.
+ *   XDK_DEPENDENT_LAUNCH  the kernel is launched as a programmatic dependent of the preceding kernel
+ *                         of the stream: it is scheduled while that kernel drains, and waits for that
+ *                         kernel's completion on the device before it reads an activation or index
+ *                         operand or writes any output.  The caller promises that the CONSTANT
+ *                         operands of the call -- projection weights, packed codes, scales, bias,
+ *                         norm weight, cos/sin tables -- were not written by the preceding kernel;
+ *                         the W4A16 tensor-core kernel starts fetching them before that wait.
+ *                         Works eagerly and under stream capture.
+ */
+#define XDK_STRICT_FP32 0x1u
+#define XDK_DEPENDENT_LAUNCH 0x2u
+
+/*
+ * Multi-GPU output descriptor (no counterpart in the reference, which is single-GPU).  A column-sharded
+ * projection on rank r computes columns [col0, col0 + n) of a [rows, ld] matrix; the *_peer entry points
+ * store every value into all `world` destinations -- the same matrix in each rank's peer-mapped buffer
+ * (xdk_peer_alloc / xdk_peer_open) -- from the kernel's epilogue, with ordinary global stores over NVLink.
+ * world = 1 with ptr[0] = y, ld = n, col0 = 0 is the plain single-GPU call.
+ */
+#define XDK_MAX_PEERS 8
+#define XDK_PEER_FLAG_BYTES 8192 /* head of every arena, reserved for the barrier flags */
+typedef struct xdk_peer_out {
+  void* ptr[XDK_MAX_PEERS]; /* destination matrix base on rank 0 .. world-1 (device pointers valid on THIS device) */
+  int32_t world;
+  int32_t reserved;
+  int64_t ld;   /* elements between consecutive rows of the destination */
+  int64_t col0; /* first destination column of this call's columns */
+} xdk_peer_out;
+
 /* Human-readable text for a status code (static storage). */
 XDK_API const char* xdk_strerror(int status);
 /* XDK_ABI_VERSION the library was built with. */
@@ -56,9 +93,18 @@ XDK_API int xdk_last_cuda_error(void);
  * Kernels that wait on mbarriers (the TMA-fed projection kernels) bound every wait by wall time; a wait
  * that gives up makes the kernel skip the work, set a bit here and return normally, so a lost copy can
  * never hang the GPU.  Returns the OR of those bits on the current device since the library was loaded
- * (bits 0-7: FP32 projection, 8-15: W4A16); 0 means no wait ever gave up.  Synchronises the device.
+ * (bits 0-6: FP32 tile-stream projection, 8-14: W4A16 kernels, 16-22: FP32 tensor-core
+ * projection; bit 31: a fault word could not be read back, treat as
+ * unhealthy); 0 means no wait ever gave up.  Synchronises the device.  xdk_peer_fault_flags() is the
+ * same for the multi-GPU flag barrier: bit p set = a wait on rank p ran out of time.
  */
 XDK_API unsigned xdk_fault_flags(void);
+XDK_API unsigned xdk_peer_fault_flags(void);
+/*
+ * Launches a kernel that does nothing (one warp): the cost of one kernel node on this stream or in a captured
+ * graph, i.e. the floor under every per-call time the benchmarks report.  No counterpart in the reference.
+ */
+XDK_API int xdk_noop(unsigned flags, void* stream);
 /* XDK_OK when `device` exists and is compute capability 10.x, else XDK_ERR_ARCH/ARG. */
 XDK_API int xdk_device_supported(int device);
 
@@ -74,6 +120,8 @@ XDK_API int xdk_device_supported(int device);
  */
 XDK_API int xdk_rmsnorm(const void* x, const void* residual, const void* weight, void* y, void* residual_out,
                 int64_t rows, int64_t hidden, float eps, int dtype, void* stream);
+XDK_API int xdk_rmsnorm_v2(const void* x, const void* residual, const void* weight, void* y, void* residual_out,
+                   int64_t rows, int64_t hidden, float eps, int dtype, unsigned flags, void* stream);
 
 /*
  * FP32 decode projection  y[M,N] = x[M,K] * W (+ bias[N]).
@@ -83,11 +131,13 @@ XDK_API int xdk_rmsnorm(const void* x, const void* residual, const void* weight,
  * order inside one launch (thread-block cluster, distributed shared memory);
  * bias is added once, after the reduction.  Those kernels accumulate with FP32 FMAs.
  * split_k = 0 lets the library pick, and for 4 < M <= 16 the choice depends on `scratch`:
- *   scratch == NULL: a large projection (K % 64 == 0, 16-byte aligned x and w, N % 4 == 0 for KN
- *     weights, K*N >= 4M) runs on the tensor cores: every operand is split into two TF32 numbers and
+ *   scratch == NULL: a large projection (K % 64 == 0, K <= 16384, 16-byte aligned x and w, N % 4 == 0
+ *     for KN weights, K*N >= 4M) runs on the tensor cores: every operand is split into two TF32 numbers and
  *     the product formed as hi*hi + hi*lo + lo*hi with FP32 accumulation.  Against an FP64 product
- *     the relative L2 error is ~2e-6 at K = 4096, inside the projection's gate (1e-5) but not the
- *     FP32-FMA result bit for bit.  Other shapes use the cluster kernels.
+ *     the relative L2 error is ~2e-6 at K = 4096 and below the projection's gate (1e-5) for every K the
+ *     path takes (longer rows stay on FP32 FMAs), but it is not the FP32-FMA result bit for bit, and an
+ *     infinity in x or W yields NaN where FP32 FMAs yield an infinity (lo = v - hi is NaN for v = inf).
+ *     Other shapes use the cluster kernels.
  *   scratch != NULL (device memory, >= xdk_gemv_scratch_bytes(...), 16-byte aligned, written and
  *     read inside the call only -- no initialisation, no state): strict FP32 FMA arithmetic on a
  *     persistent tile-stream kernel that deals the weight tiles evenly to all SMs.  Calls that
@@ -102,6 +152,15 @@ XDK_API int xdk_rmsnorm(const void* x, const void* residual, const void* weight,
 XDK_API int xdk_gemv_f32(const float* x, const float* w, const float* bias, float* y,
                  int64_t m, int64_t k, int64_t n, int weight_is_nk, int split_k,
                  void* scratch, size_t scratch_bytes, void* stream);
+/*
+ * Version 2: the arithmetic is chosen by `flags`, not by the scratch pointer.  With XDK_STRICT_FP32 the
+ * call never leaves FP32 FMA arithmetic; scratch (optional, same rules as above) then only lets a large
+ * 4 < M <= 16 projection (K*N >= 48M) use the balanced tile-stream kernel instead of the cluster
+ * kernels.  Without the flag, scratch is ignored whenever the tensor-core kernel takes the shape.
+ */
+XDK_API int xdk_gemv_f32_v2(const float* x, const float* w, const float* bias, float* y,
+                    int64_t m, int64_t k, int64_t n, int weight_is_nk, int split_k,
+                    void* scratch, size_t scratch_bytes, unsigned flags, void* stream);
 /*
  * Introspection (no counterpart in the reference): would xdk_gemv_f32(split_k = 0, scratch = NULL) with 16-byte
  * aligned x and w run this shape on the tensor-core kernel, and with what launch?  Returns 1 and fills
@@ -158,6 +217,13 @@ XDK_API int xdk_rope_kv_append(const void* q, const void* k, const void* v, cons
                        int64_t cos_width, int64_t max_pages_per_seq, int64_t page_size, int64_t rope_dim,
                        int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
                        int interleaved, int cache_is_hnd, int dtype, void* stream);
+XDK_API int xdk_rope_kv_append_v2(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                       const int64_t* positions, const int64_t* page_table, const int64_t* sequence_ids,
+                       void* q_out, void* k_cache, void* v_cache,
+                       int64_t tokens, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                       int64_t cos_width, int64_t max_pages_per_seq, int64_t page_size, int64_t rope_dim,
+                       int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
+                       int interleaved, int cache_is_hnd, int dtype, unsigned flags, void* stream);
 
 /*
  * W4A16 projection  y[M,N] = half( x[M,K] * W^T (+ bias[N]) ), FP32 accumulation.
@@ -170,6 +236,56 @@ XDK_API int xdk_rope_kv_append(const void* q, const void* k, const void* v, cons
  */
 XDK_API int xdk_w4a16(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
               int64_t m, int64_t k, int64_t n, int group_size, void* stream);
+XDK_API int xdk_w4a16_v2(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
+                 int64_t m, int64_t k, int64_t n, int group_size, unsigned flags, void* stream);
+
+/*
+ * Symmetric INT4 quantisation on the device, into the format xdk_w4a16 reads: weight [n, k] row-major of
+ * `dtype` (FP32, BF16 or FP16) -> packed uint8 [n, ceil(k/2)] and FP16 scales [n, ceil(k/group_size)].
+ * Per (row, group): scale = half(max|w| / 7) (at least 2^-24; 1 for an all-zero group), rounded to FP16
+ * BEFORE q = clamp(round-half-even(w / scale), -7, 7) is chosen; code = q + 8.  Packed bytes and scales are
+ * bit-identical to the host function.  *status (device int32, zero it first) receives the OR of
+ * 1 = a weight is not finite, 2 = a scale is not representable in FP16, 4 = a dequantised weight is not
+ * representable in FP16 -- the three conditions the host function raises on; read it after the stream drained.
+ * Replaces the set-up step quantize_int4 (src/crossdsl_kernels/quantization.py:39-63) for weights that
+ * already live on the device.
+ */
+XDK_API int xdk_quantize_int4(const void* weight, int dtype, int64_t n, int64_t k, int group_size, uint8_t* packed,
+                      void* scales, int* status, void* stream);
+
+/*
+ * Multi-GPU plumbing, one process per GPU on one node (no upstream counterpart).
+ * xdk_peer_alloc: a zeroed cudaMalloc arena of `bytes` (>= XDK_PEER_FLAG_BYTES; the head of that size holds the
+ *   barrier flags, payload starts behind it).  This and xdk_peer_free are the only entry points that allocate.
+ * xdk_peer_export / xdk_peer_open / xdk_peer_close: the arena as a 64-byte CUDA IPC handle, and another
+ *   process's handle mapped into this one (peer access is enabled on first use).
+ * xdk_peer_barrier: launched by EVERY rank on its stream after the kernels that stored into the peers' arenas:
+ *   publishes this rank's next epoch for `site` (0..63; use one site per exchange point of a step) to every
+ *   arena and waits until all `world` ranks have published it, at most timeout_us microseconds (0: one second).
+ *   arenas[p] = rank p's arena as mapped here (arenas[rank] = the local one).  A wait that runs out sets bit p
+ *   of xdk_peer_fault_flags() and the kernel returns normally.  Epochs live on the device, so the launch can be
+ *   captured in a CUDA graph and replayed -- by all ranks equally often.
+ */
+XDK_API int xdk_peer_alloc(size_t bytes, void** ptr);
+XDK_API int xdk_peer_free(void* ptr);
+XDK_API int xdk_peer_export(void* ptr, void* handle64);
+XDK_API int xdk_peer_open(const void* handle64, void** ptr);
+XDK_API int xdk_peer_close(void* ptr);
+XDK_API int xdk_peer_barrier(void* const* arenas, int rank, int world, int site, unsigned timeout_us, unsigned flags,
+                     void* stream);
+/* The projections and the append with their output (rotated Q for the append) stored into every rank's buffer. */
+XDK_API int xdk_gemv_f32_peer(const float* x, const float* w, const float* bias, const xdk_peer_out* y,
+                      int64_t m, int64_t k, int64_t n, int weight_is_nk, int split_k,
+                      void* scratch, size_t scratch_bytes, unsigned flags, void* stream);
+XDK_API int xdk_w4a16_peer(const void* x, const uint8_t* packed, const void* scales, const void* bias,
+                   const xdk_peer_out* y, int64_t m, int64_t k, int64_t n, int group_size, unsigned flags, void* stream);
+XDK_API int xdk_rope_kv_append_peer(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                       const int64_t* positions, const int64_t* page_table, const int64_t* sequence_ids,
+                       const xdk_peer_out* q_out, void* k_cache, void* v_cache,
+                       int64_t tokens, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                       int64_t cos_width, int64_t max_pages_per_seq, int64_t page_size, int64_t rope_dim,
+                       int64_t q_token_stride, int64_t k_token_stride, int64_t v_token_stride,
+                       int interleaved, int cache_is_hnd, int dtype, unsigned flags, void* stream);
 
 /*
  * Multi-GPU helper with no upstream counterpart (upstream is single-GPU): after an all-gather of

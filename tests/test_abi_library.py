@@ -31,7 +31,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 
 def test_status_text_and_version():
     lib = _native.lib()
-    assert lib.xdk_abi_version() == 1
+    assert lib.xdk_abi_version() == 2
     assert lib.xdk_strerror(0) == b"ok"
     for code in (-1, -2, -3, -4, -99):
         assert len(lib.xdk_strerror(code)) > 0
@@ -50,7 +50,7 @@ def test_header_is_plain_c_and_a_c_program_links(tmp_path):
         '#include <stdio.h>\n#include <stdint.h>\n#include "xdk_b200.h"\n'
         "int main(void) {\n"
         "  int32_t plan[5];\n"
-        "  if (xdk_abi_version() != 1) return 1;\n"
+        "  if (xdk_abi_version() != 2) return 1;\n"
         "  if (xdk_gemv_tc_plan(16, 4096, 14336, 0, plan) != 1) return 2;\n"
         '  printf("%s %d %d\\n", xdk_strerror(XDK_OK), (int)plan[0], (int)plan[1]);\n'
         "  return 0;\n}\n")

@@ -161,6 +161,40 @@ def test_graph_replay_follows_changed_inputs_on_side_stream():
     gate(gy, x2, w_kn, b, 1024)
 
 
+@pytest.mark.parametrize("layout", ["KN", "NK"])
+@pytest.mark.parametrize("k", [14336, 16384, 32768])
+def test_tensor_core_path_at_large_k(layout, k):
+    """The split-TF32 accumulation error grows with the number of products an accumulator sums, so the gate is
+    checked at the largest K the tensor-core path takes (16384), at the MLP-down projection of the model the
+    decode-layer chain is shaped on (14336), and beyond the cap (32768 runs on FP32 FMAs)."""
+    from cross_dsl_kernels_b200.ops import decode_linear
+    m, n = 16, 4096
+    x, w, b, w_kn = make(m, k, n, layout, True, seed=k)
+    y = decode_linear(x.cuda(), w.cuda(), b.cuda(), weight_layout=layout)
+    gate(y, x, w_kn, b, k)
+    import ctypes
+    from cross_dsl_kernels_b200 import _native
+    plan = (ctypes.c_int32 * 5)()
+    assert _native.lib().xdk_gemv_tc_plan(m, k, n, int(layout == "NK"), plan) == (1 if k <= 16384 else 0)
+
+
+def test_tensor_core_path_on_same_sign_and_wide_range_operands():
+    """All-positive operands (post-activation inputs) expose a one-sided truncation bias that zero-mean data hide;
+    a wide exponent spread exercises the lo halves.  Same gate."""
+    from cross_dsl_kernels_b200.ops import decode_linear
+    g = torch.Generator().manual_seed(11)
+    m, k, n = 16, 4096, 4096
+    x = torch.rand(m, k, generator=g) + 0.1
+    w_kn = (torch.rand(k, n, generator=g) + 0.1) / k
+    y = decode_linear(x.cuda(), w_kn.cuda())
+    gate(y, x, w_kn, None, k)
+    x2 = torch.randn(m, k, generator=g) * torch.exp2(torch.randint(-12, 12, (m, k), generator=g).float())
+    w2 = torch.randn(k, n, generator=g) * torch.exp2(torch.randint(-12, 12, (k, n), generator=g).float()) / k ** 0.5
+    want = x2.double() @ w2.double()
+    y2 = decode_linear(x2.cuda(), w2.cuda())
+    assert rel_l2(y2.cpu(), want) <= 1e-5
+
+
 def test_rejections():
     from cross_dsl_kernels_b200.ops import decode_linear
     x, w, b, _ = make(2, 64, 32, "KN", True)

@@ -162,3 +162,42 @@ def test_both_m16_paths_match_oracle_in_a_fresh_process(force):
     env = dict(os.environ, XDK_W4A16_UMMA=force)
     done = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0 and "umma ok" in done.stdout, done.stdout + done.stderr
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,k,group", [(64, 4096, 128), (5, 257, 32), (3, 1000, 256), (2, 64, 64), (1, 1, 32)])
+def test_device_quantiser_is_bit_identical_to_the_host_function(dtype, n, k, group):
+    """xdk_quantize_int4 against quantize_int4 on the CPU (which the golden fixture pins to upstream's own
+    output): same packed bytes, same FP16 scales; all-zero groups get scale 1."""
+    g = torch.Generator().manual_seed(n * 1000 + k)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(dtype)
+    if k >= group:
+        w[0, :group] = 0  # an all-zero group
+    w[-1, -1] = w.abs().max() * 3  # a clear peak at the ragged end
+    want_p, want_s = qz.quantize_int4(w, group)
+    got_p, got_s = qz.quantize_int4_device(w.cuda(), group)
+    assert torch.equal(got_p.cpu(), want_p)
+    assert torch.equal(got_s.cpu().view(torch.int16), want_s.view(torch.int16))
+
+
+def test_device_quantiser_reports_what_the_host_function_raises_on():
+    w = torch.randn(4, 256)
+    bad = w.clone()
+    bad[1, 7] = float("inf")
+    with pytest.raises(ValueError, match="finite"):
+        qz.quantize_int4_device(bad.cuda(), 128)
+    huge = w.clone() * 1e6  # peak / 7 overflows FP16
+    with pytest.raises(ValueError, match="FP16"):
+        qz.quantize_int4_device(huge.cuda(), 128)
+    with pytest.raises(ValueError):
+        qz.quantize_int4_device(w, 128)  # a CPU tensor
+
+
+def test_quantise_then_project_round_trip_on_the_device():
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(512, 1024, generator=g) * 0.02
+    x = torch.randn(16, 1024, generator=g).half()
+    packed, scales = qz.quantize_int4_device(w.cuda(), 128)
+    y = w4a16_linear(x.cuda(), packed, scales, None, group_size=128)
+    gate(y, x, packed.cpu(), scales.cpu(), None, 128)

@@ -172,3 +172,19 @@ def test_cache_overlap_guard():
     with pytest.raises(ValueError, match="overlap"):
         contracts.validate_cache_storage((storage[20:24],), a, b)
     contracts.validate_cache_storage((storage[:0],), a, b)  # empty tensors never overlap
+
+
+def test_cache_overlap_guard_sees_the_whole_span_of_a_strided_input():
+    # q is a column slice of a fused [tokens, 96] QKV matrix: 4 rows of 32 elements, 96 apart.  Its numel
+    # (128) covers only the first row and a third; a cache placed over the LAST row must still be refused.
+    from cross_dsl_kernels_b200 import contracts
+    storage = torch.zeros(4 * 96 + 64)
+    qkv = storage[: 4 * 96].view(4, 96)
+    q = qkv[:, :32].view(4, 2, 16)
+    assert not q.is_contiguous()
+    cache_on_last_row = storage[3 * 96: 3 * 96 + 16]
+    elsewhere = storage[4 * 96: 4 * 96 + 16]
+    other = torch.zeros(16)
+    with pytest.raises(ValueError, match="overlap"):
+        contracts.validate_cache_storage((q,), cache_on_last_row, other)
+    contracts.validate_cache_storage((q,), elsewhere, other)
