@@ -68,39 +68,6 @@ __device__ __forceinline__ void dequant8(uint32_t word, __half2 scale2, __half2 
   w[3] = __hmul2(q3, scale2);
 }
 
-// The same four half2, bit for bit, in fewer instructions when scale * 2^20 is finite (scale < 2^-4): a code masked
-// into bits 4..7 of a 16-bit lane with a zero exponent field IS the FP16 subnormal code * 2^-20, so one packed FMA
-// gives fma(code * 2^-20, scale * 2^20, -8 * scale) = round((code - 8) * scale) with a single rounding -- the
-// product and the addend are exact.  One byte permute, two multiplies by 16 (FMA pipe), four masks, four FMAs.
-__device__ __forceinline__ void dequant8_fma(uint32_t word, __half2 s20, __half2 m8s, __half2 (&w)[4]) {
-  constexpr uint32_t kMask = 0x00f000f0u;
-  const uint32_t sw = __byte_perm(word, 0, 0x2301);  // bytes (1,0,3,2): codes 2,3 / 6,7 into the low byte of each lane
-  uint32_t w16, s16;
-  asm("mul.lo.u32 %0, %1, 16;" : "=r"(w16) : "r"(word));
-  asm("mul.lo.u32 %0, %1, 16;" : "=r"(s16) : "r"(sw));
-  const uint32_t a0 = w16 & kMask, a1 = word & kMask, a2 = s16 & kMask, a3 = sw & kMask;
-  w[0] = __hfma2(*reinterpret_cast<const __half2*>(&a0), s20, m8s);
-  w[1] = __hfma2(*reinterpret_cast<const __half2*>(&a1), s20, m8s);
-  w[2] = __hfma2(*reinterpret_cast<const __half2*>(&a2), s20, m8s);
-  w[3] = __hfma2(*reinterpret_cast<const __half2*>(&a3), s20, m8s);
-}
-// A scale prepared for either path: `fast` when scale * 2^20 is finite.
-struct PreparedScale {
-  __half2 s2, s20, m8s;
-  bool fast;
-  __device__ __forceinline__ void set(__half scale) {
-    const __half big = __hmul(__hmul(scale, __float2half(1024.0f)), __float2half(1024.0f));  // exact, or inf
-    fast = (__half_as_ushort(big) & 0x7fffu) < 0x7c00u;
-    s2 = __half2half2(scale);
-    s20 = __half2half2(big);
-    m8s = __half2half2(__hmul(scale, __float2half(-8.0f)));
-  }
-  __device__ __forceinline__ void dequant(uint32_t word, __half2 (&w)[4]) const {
-    if (fast) dequant8_fma(word, s20, m8s, w);
-    else dequant8(word, s2, w);
-  }
-};
-
 // acc += a * b with FP16 operands and an FP32 accumulator in one instruction (sm_100 mixed FMA).
 __device__ __forceinline__ void fma_h(float& acc, __half a, __half b) {
   asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)));
@@ -161,6 +128,7 @@ w4a16_simt_kernel(W4Args a) {
         const int v = v0 + u * 32 + lane;
         if (v0 + u * 32 < vecs) {
           const int vv = v < vecs ? v : 0;  // out-of-range lanes multiply zeros by valid x
+#pragma unroll
 #pragma unroll
           for (int j = 0; j < 4; ++j) {  // the four 32-bit words of the vector, 8 k each
             __half2 w[CW][4];
@@ -794,7 +762,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
     const int c = lq * 32 + lane;             // this thread's TMEM lane
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(lq * 32) << 16);
     const uint32_t a_lane_base = lane_base + kUTmemA + kh * (kUStageCols / 2);
-    const unsigned char* sc_row = scbuf + c * scale_row_bytes;  // groups % 8 == 0: 16-byte aligned, whole 16-byte blocks
+    const __half* sc_row = reinterpret_cast<const __half*>(scbuf + c * scale_row_bytes);
     int strip_i = 0;
     bool ok = true;
     while (cur.begin_strip()) {
@@ -805,8 +773,6 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       const int k_range0 = ks * cur.kper;
       const int split = cur.split;
       if (ok) ok = mbar_wait(sc_full, strip_i & 1);
-      U4 sc8 = U4{0u, 0u, 0u, 0u};  // scales of groups [8 sc_blk, 8 sc_blk + 8) of this column
-      int sc_blk = -1;
       do {
         const int buf = cur.q % kUPackedBufs, s = cur.q % kUStages;
         if (ok) ok = mbar_wait(pk_full + buf, (cur.q / kUPackedBufs) & 1);
@@ -817,20 +783,10 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
           // lanes of a warp, which read the same piece of 32 different rows, spread over all bank groups
           const unsigned char* row = packed + buf * kUPackedBytes + c * (kUStepK / 2);
           const int k_half = k_range0 + cur.kc * kUStepK + kh * (kUStepK / 2);
-          PreparedScale ps;
 #pragma unroll
           for (int pc = 0; pc < kUStepK / 64; ++pc) {
-            if ((pc & 1) == 0) {
-              // two pieces = 64 k lie inside one group (group >= 64).  The scales of 8 consecutive groups come with
-              // one 16-byte shared load (a per-scale read of this [lane][groups] array is a 16-way bank conflict).
-              const int g = (k_half + pc * 32) >> scale_shift;
-              if ((g >> 3) != sc_blk) {
-                sc_blk = g >> 3;
-                sc8 = *reinterpret_cast<const U4*>(sc_row + sc_blk * 16);
-              }
-              const uint32_t w2 = (g & 4) ? ((g & 2) ? sc8.w : sc8.z) : ((g & 2) ? sc8.y : sc8.x);
-              ps.set(__ushort_as_half(static_cast<unsigned short>((g & 1) ? (w2 >> 16) : (w2 & 0xffffu))));
-            }
+            // two pieces = 64 k lie inside one group (group >= 64)
+            const __half2 s2 = __half2half2(sc_row[(k_half + (pc & ~1) * 32) >> scale_shift]);
             const int piece = kh * (kUStepK / 64) + pc;
             const U4 wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));  // rows past N are zero-filled: harmless
             uint32_t r[16];
@@ -838,7 +794,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
             for (int w = 0; w < 4; ++w) {
               const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
               __half2 h[4];
-              ps.dequant(word, h);
+              dequant8(word, s2, h);
 #pragma unroll
               for (int i = 0; i < 4; ++i) r[4 * w + i] = *reinterpret_cast<uint32_t*>(&h[i]);
             }

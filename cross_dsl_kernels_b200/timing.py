@@ -70,7 +70,8 @@ def _poison(obj) -> None:
 
 
 def graph_median_us(calls: Sequence[Callable[[], object]], replays: int = 20, warmup: int = 3,
-                    check: Callable[[str, object], None] | None = None, mutate: Callable[[], None] | None = None) -> dict:
+                    check: Callable[[str, object], None] | None = None, mutate: Callable[[], None] | None = None,
+                    poison: Callable[[list], None] | None = None) -> dict:
     """Per-call median of a graph of back-to-back calls.
 
     ``check(stage, output_of_call_0)`` (optional) is the gate, and it raises on a mismatch.  It runs three times:
@@ -78,7 +79,8 @@ def graph_median_us(calls: Sequence[Callable[[], object]], replays: int = 20, wa
     after a replay whose output buffers were filled with NaN first (a replay that silently does nothing fails);
     ``"changed"`` after ``mutate()`` has changed the INPUT contents of call 0 in place at their fixed addresses and
     the graph was replayed again (a graph that baked values in instead of addresses fails).  ``mutate`` is then
-    called a second time and must restore the inputs.  This is the discipline of upstream's
+    called a second time and must restore the inputs.  ``poison(outputs)`` replaces the default (NaN into every
+    floating-point output) for ops whose outputs are not all freshly written, such as a cache that keeps a sentinel.  This is the discipline of upstream's
     benchmarks/compare.py:28-41, 247-258 and benchmarks/gemv_cuda_benchmark.py:97-126."""
     if check is not None:
         first = calls[0]()
@@ -87,13 +89,14 @@ def graph_median_us(calls: Sequence[Callable[[], object]], replays: int = 20, wa
     outputs: list = []
     graph = capture(calls, outputs=outputs)
     if check is not None:
-        _poison(outputs)
+        poison = poison or _poison
+        poison(outputs)
         graph.replay()
         torch.cuda.synchronize()
         check("poisoned", outputs[0])
         if mutate is not None:
             mutate()
-            _poison(outputs)
+            poison(outputs)
             graph.replay()
             torch.cuda.synchronize()
             check("changed", outputs[0])
