@@ -392,6 +392,8 @@ def main() -> None:
 
     mark("start")
     torch.cuda.set_device(local_rank)
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"  # NCCL prints its version banner on stdout, which must carry one JSON line only
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         mark("process group ready")
@@ -610,6 +612,9 @@ def main() -> None:
         for exchange, dependent in modes:
             chain_rows.append(kernel_bench.bench_chain(rank=rank, world=world, peak=peaks["hbm_gbs"], exchange=exchange,
                                                        dependent=dependent, check=chain_gate(rank, world)))
+        if world == 1:  # the layer with the two ops that follow the path: attention over the cache, SwiGLU
+            chain_rows.append(kernel_bench.bench_chain(peak=peaks["hbm_gbs"], dependent=True, attention=True,
+                                                       check=chain_gate(rank, world)))
         mark("chain done")
 
     faults = _native.fault_flags() | (arena.fault_flags() << 0 if arena is not None else 0)
@@ -652,6 +657,15 @@ def chain_gate(rank: int, world: int):
         c = chain.cfg
         if world == 1:
             L = chain.host_weights(len(chain.layers) - 1)
+            if chain.attention:
+                from oracle import attention as oracle_attention
+
+                dv = chain.dev
+                want = oracle_attention.paged_decode_attention(out["q_rot"].cpu(), chain.k_cache.cpu(), chain.v_cache.cpu(),
+                                                               dv["positions"].cpu(), dv["page_table"].cpu(),
+                                                               dv["sequence_ids"].cpu(), page_size=c.page_size)
+                _need(_rel_l2(out["attn"].cpu().float(), want.view(c.tokens, c.hidden).float()) <= 2e-3, "chain: attention read differs")
+                _need(_ulps16(out["act"].cpu(), oracle_attention.swiglu(out["up_all"].cpu())) <= 1, "chain: SwiGLU more than one ulp off")
             n2_want, _ = decode_ops.residual_rmsnorm(out["attn"].cpu(), out["r1"].cpu(), L["w2"], c.eps)
             _need(_ulps16(out["n2"].cpu(), n2_want) <= 1, "chain: second norm more than one ulp off")
             ref = int4.w4a16_projection(out["n2"].cpu(), L["up_packed"], L["up_scales"], None, group_size=c.group).double()

@@ -39,6 +39,8 @@ SIGNATURES = {
     "xdk_rope_kv_append_v2": (_int, [_p] * 11 + [_i64] * 11 + [_int, _int, _int, _uint, _p]),
     "xdk_w4a16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _p]),
     "xdk_w4a16_v2": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _uint, _p]),
+    "xdk_paged_decode_attention": (_int, [_p] * 7 + [_i64] * 6 + [_int, ctypes.c_float, _i64, _int, _uint, _p]),
+    "xdk_swiglu": (_int, [_p, _p, _i64, _i64, _i64, _i64, _int, _uint, _p]),
     "xdk_quantize_int4": (_int, [_p, _int, _i64, _i64, _int, _p, _p, _p, _p]),
     "xdk_peer_fault_flags": (ctypes.c_uint, []),
     "xdk_peer_alloc": (_int, [ctypes.c_size_t, _p]),

@@ -18,7 +18,7 @@ import sys
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libxdk_b200.so"
-SOURCES = ("abi.cu", "rmsnorm.cu", "gemv.cu", "gemv_tc.cu", "rope_kv.cu", "w4a16.cu", "quantize.cu", "peer.cu", "unshard.cu")
+SOURCES = ("abi.cu", "rmsnorm.cu", "gemv.cu", "gemv_tc.cu", "rope_kv.cu", "w4a16.cu", "quantize.cu", "peer.cu", "swiglu.cu", "attention.cu", "unshard.cu")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 
 

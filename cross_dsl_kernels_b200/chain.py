@@ -8,9 +8,13 @@ Per layer and decode step (batch of ``tokens`` rows, FP16 activations):
 4. residual RMSNorm                     (rotated q as the hidden stream, r1) -> (n2, r2)
 5. W4A16 MLP up+gate projection         n2 -> upgate [tokens, 2 * mlp]
 
-No attention sits between 3 and 4 (it is not one of the four kernels), so the
-rotated Q -- which has the hidden width -- stands in for the attention output
-and keeps the five launches data-dependent.
+The five-kernel chain has no attention between 3 and 4 (it is not one of the
+four kernels): the rotated Q -- which has the hidden width -- stands in for the
+attention output and keeps the five launches data-dependent.  With
+``attention=True`` (single GPU) the two ops that follow the path are inserted:
+
+3b. paged decode attention over the cache step 3 wrote   q_rot -> attn [tokens, hidden]
+5b. SwiGLU on the up+gate output                          upgate -> act [tokens, mlp]
 
 Multi-GPU (one process per GPU): the projections are column-sharded and the KV
 heads split, rank r owning q heads [r*Hq/g, ...), kv heads [r*Hkv/g, ...) and
@@ -117,13 +121,17 @@ class DecodeLayerChain:
     """Weights, caches and index tensors of ``layers`` identical-shape layers for one rank."""
 
     def __init__(self, cfg: ChainConfig = ChainConfig(), *, layers: int = 1, rank: int = 0, world: int = 1,
-                 seed: int = 0, device="cuda", group=None, exchange: str = "peer", dependent_launch: bool = False):
+                 seed: int = 0, device="cuda", group=None, exchange: str = "peer", dependent_launch: bool = False,
+                 attention: bool = False):
         if cfg.q_heads % world or cfg.kv_heads % world or (2 * cfg.mlp) % world:
             raise ValueError("heads and MLP columns must divide by the number of ranks")
         if exchange not in ("peer", "nccl"):
             raise ValueError("exchange must be 'peer' or 'nccl'")
+        if attention and world > 1:
+            raise ValueError("the attention read is built for the single-GPU chain only")
         self.cfg, self.rank, self.world, self.pg = cfg, rank, world, group
         self.exchange, self.dependent = exchange, bool(dependent_launch)
+        self.attention = bool(attention)
         self.device = torch.device(device)
         c = cfg
         # Weights are drawn on the device (Philox, same values on every rank for one seed): drawing
@@ -182,7 +190,7 @@ class DecodeLayerChain:
             self.up_full = torch.empty(c.tokens, 2 * c.mlp, dtype=torch.float16, device=self.device)
             self.launches_per_layer = 7  # five kernels + two re-layout kernels (+ two NCCL all-gathers)
         else:
-            self.launches_per_layer = 5
+            self.launches_per_layer = 7 if attention else 5
 
     def host_weights(self, layer: int = 0) -> dict:
         """CPU copies of one layer's unsharded weights (single-rank chains only; for checkers)."""
@@ -214,6 +222,11 @@ class DecodeLayerChain:
         elif self.world > 1:
             dist.all_gather_into_tensor(self.q_gather, q_rot.view(c.tokens, hq * d), group=self.pg)
             attn = unshard_columns(self.q_gather, self.q_full)
+        elif self.attention:
+            from .ops import paged_decode_attention
+
+            attn = paged_decode_attention(q_rot, self.k_cache, self.v_cache, dv["positions"], dv["page_table"], dv["sequence_ids"],
+                                          page_size=c.page_size, context_hint=c.context, dependent_launch=dep).view(c.tokens, c.hidden)
         else:
             attn = q_rot.view(c.tokens, c.hidden)
         n2, r2 = fused_residual_rmsnorm(attn, r1, L["w2"], c.eps, dependent_launch=dep)
@@ -231,7 +244,12 @@ class DecodeLayerChain:
                 up_all = unshard_columns(self.up_gather, self.up_full)
             else:
                 up_all = up
-        return dict(n1=n1, r1=r1, qkv=qkv, q_rot=q_rot, attn=attn, n2=n2, r2=r2, up=up, up_all=up_all)
+        out = dict(n1=n1, r1=r1, qkv=qkv, q_rot=q_rot, attn=attn, n2=n2, r2=r2, up=up, up_all=up_all)
+        if self.attention:
+            from .ops import swiglu
+
+            out["act"] = swiglu(up_all, dependent_launch=dep)
+        return out
 
     def run_layers(self):
         """All layers back to back, each feeding the next its (n2, r2)."""

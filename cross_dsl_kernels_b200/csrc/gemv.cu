@@ -632,6 +632,8 @@ static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 // In host code the name above is only a stand-in for the symbol; the address a kernel can use has to
 // be asked for, per device, with that device current.
 float* static_scratch_for_current_device(int* status) {
+  // Filled without locking: host threads that race here all store the same address.  Not refreshed after a
+  // cudaDeviceReset() (the header says so).
   static float* address[64];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {

@@ -18,7 +18,11 @@
 // 32-column units and walks it in strips of <= 4 units, full K each; narrow strips split K S ways over the TMEM
 // lane quarters and add the S partial sums through shared memory in a fixed order; S is one value per launch
 // (4 when no CTA has more than one unit, 2 for two, else 1), which also sizes the x buffers, and whatever shared
-// memory they leave goes to the W ring.
+// memory they leave goes to the W ring.  A projection with fewer units than half the SMs (a column shard of a
+// multi-GPU run) is additionally split along K over the 2 or 4 CTAs of a thread-block cluster: every CTA of the
+// cluster walks the same strips over its own part of K, the parts store their partial sums into the rank-0 CTA's
+// shared memory (distributed shared memory, mbarrier hand-off with bounded waits) and rank 0 adds them in rank
+// order, so the result stays deterministic.
 //   TMA warps (4)      : one lane each, one warp per TMEM lane quarter: the W tile of a 64-k step (NK: two 128-byte
 //                        swizzled [32 columns][32 k] boxes per quarter; KN: one [64 k][32 u columns] box per k range,
 //                        u = units of the strip, so that HBM sees runs of up to 512 bytes) into a ring of step buffers.  Four warps because a warp gets a TMA box copy out only every ~230
@@ -64,6 +68,7 @@ constexpr int kXHalf1 = 2 * kXSbo;              // hi (or lo) image of one k ran
 constexpr int kXRaw1 = 16 * kStepK * 4;         // one k range of [16 rows][64 k] as TMA lands it
 constexpr int kXBufs = 2;
 constexpr int kRedBytes = 128 * 16 * 4;         // k-range partials: [lane][16] floats
+constexpr int kMaxParts = 4;                    // CTAs of a cluster sharing a strip along K
 constexpr int kWTma = 8, kWX0 = 12, kWMma0 = 14;  // warp roles; 0-7 split, 8-11 TMA, 12-13 x, 14-17 MMA
 constexpr int kThreads = (kWMma0 + kMaxIssuers) * 32;
 constexpr uint32_t kHiMask = 0xffffe000u;       // keeps sign, exponent and the 10 mantissa bits TF32 uses
@@ -75,6 +80,7 @@ struct TcArgs {
   int ctas, total_units;
   int split;  // k ranges per strip (1, 2, 4), the same for every strip of the launch
   int ring;   // W step buffers
+  int kparts; // CTAs of a cluster that share every strip, each walking K / kparts (1, 2, 4); grid = (ctas, kparts)
 };
 
 __device__ __forceinline__ void split_tf32(uint32_t v, uint32_t& hi, uint32_t& lo) {
@@ -95,7 +101,9 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
   unsigned char* xbuf = ring + kRing * kStepBytes;           // [kXBufs][hi image | lo image], 16 S rows each
   unsigned char* xraw = xbuf + kXBufs * kXBytes;             // [kXBufs][16 rows][S k ranges][64 k]
   float* red = reinterpret_cast<float*>(xraw + kXBufs * kXRawBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(red) + kRedBytes);
+  // partial sums of the other CTAs of the cluster land here (in the rank-0 CTA): [part - 1][lane][16] floats
+  float* inbox = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(red) + kRedBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(inbox) + (a.kparts - 1) * kRedBytes);
   uint64_t* w_full = bars;                 // [kMaxRing] TMA bytes of a W step landed
   uint64_t* w_empty = w_full + kMaxRing;   // [kMaxRing] the 8 split warps are done with the step
   uint64_t* a_full = w_empty + kMaxRing;   // [kStages] the 8 split warps wrote the stage to TMEM
@@ -104,11 +112,17 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
   uint64_t* x_full = x_raw + kXBufs;       // [kXBufs]  the x warps wrote both operand images
   uint64_t* x_empty = x_full + kXBufs;     // [kXBufs]  every issuer's MMAs that read the images completed
   uint64_t* acc_full = x_empty + kXBufs;   // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* inbox_full = acc_full + 1;     // [1] rank 0: the other parts stored a strip's partials (128 arrivals each)
+  uint64_t* inbox_free = inbox_full + 1;   // [1] other ranks: rank 0 has read the partials of the previous strip
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(inbox_free + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // K split across the CTAs of a cluster (narrow projections: fewer 32-column units than SMs): part p walks
+  // k in [p K / kparts, (p + 1) K / kparts) of the SAME strips; rank 0 adds the parts in rank order and stores.
+  const int part = a.kparts > 1 ? static_cast<int>(blockIdx.y) : 0;
+  const int k_len = a.k / a.kparts, k_base = part * k_len;
   UmmaCursor cur;
-  cur.init(blockIdx.x, a.ctas, a.total_units, a.k, kStepK, S);
+  cur.init(blockIdx.x, a.ctas, a.total_units, k_len, kStepK, S);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kRing; ++i) {
@@ -125,11 +139,16 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
       mbar_init(a_empty + i, issuers);
     }
     mbar_init(acc_full, issuers);
+    mbar_init(inbox_full, 128 * (a.kparts - 1) > 0 ? 128 * (a.kparts - 1) : 1);
+    mbar_init(inbox_free, 1);
     mbar_fence_init();
   }
   if (warp == kWTma) tmem_alloc<kTmemCols>(tmem_slot);
   tc_fence_before();
   __syncthreads();
+  if (a.kparts > 1) {  // every CTA's barriers exist before a peer may arrive on them
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -148,7 +167,7 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
             ok = false;
             break;
           }
-          const int k0 = k_range0 + cur.kc * kStepK;
+          const int k0 = k_base + k_range0 + cur.kc * kStepK;
           if (NK) {  // two [32 columns][32 k] boxes, 128-byte rows, swizzled
             if (!live) {
               mbar_arrive_cta(w_full + buf);
@@ -220,7 +239,7 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
       if (t == 0) {
         const int xb = ahead.q % kXBufs;
         mbar_expect_tx(x_raw + xb, static_cast<unsigned>(kXRawBytes));  // rows >= M are out of range: zero-filled, still counted
-        tma_box_3d(xraw + xb * kXRawBytes, &xmap, ahead.kc * kStepK, 0, 0, x_raw + xb);  // all k ranges in one box
+        tma_box_4d(xraw + xb * kXRawBytes, &xmap, ahead.kc * kStepK, 0, part, 0, x_raw + xb);  // all k ranges in one box
       }
       if (!ahead.next_step()) ahead_live = ahead.begin_strip();
     };
@@ -348,7 +367,32 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
             for (int m = 0; m < 16; ++m) sum[m] = __fadd_rn(sum[m], red[(c + j * qpk * 32) * 16 + m]);
         }
       }
-      if (warp < 4 && ok && warp_live && ks == 0 && col < a.n) {
+      const bool owner = warp < 4 && ok && warp_live && ks == 0;  // this thread holds a column's sum over this CTA's K
+      if (a.kparts > 1 && warp < 4) {
+        if (part != 0) {
+          // hand the partial sums to the rank-0 CTA: its inbox must be free (it has read the previous strip's)
+          if (ok && strip_i > 0) ok = mbar_wait_cluster(inbox_free, (strip_i - 1) & 1);
+          if (owner) {
+            const uint32_t dst = cluster_map(inbox + (static_cast<size_t>(part - 1) * 128 + c) * 16, 0u);
+#pragma unroll
+            for (int m = 0; m < 16; m += 4) cluster_store_f4(dst + m * 4, make_float4(sum[m], sum[m + 1], sum[m + 2], sum[m + 3]));
+          }
+          cluster_arrive(cluster_map(inbox_full, 0u));  // all 128 epilogue threads arrive, with or without data
+        } else {
+          if (ok) ok = mbar_wait_cluster(inbox_full, strip_i & 1);
+          if (owner && ok) {
+            for (int p = 1; p < a.kparts; ++p)  // fixed order: part 0 + 1 + 2 + 3
+#pragma unroll
+              for (int m = 0; m < 16; ++m) sum[m] = __fadd_rn(sum[m], inbox[(static_cast<size_t>(p - 1) * 128 + c) * 16 + m]);
+          }
+          asm volatile("bar.sync 3, 128;" ::: "memory");  // warps 0-3: every inbox slot has been read
+          // Tell the other parts only when another strip follows: after their last hand-over they may have exited,
+          // and an exited CTA's shared memory must not be touched.
+          if (threadIdx.x == 0 && cur.unit < cur.unit_end)
+            for (int p = 1; p < a.kparts; ++p) cluster_arrive(cluster_map(inbox_free, static_cast<unsigned>(p)));
+        }
+      }
+      if (owner && ok && part == 0 && col < a.n) {
         const float bv = a.bias ? a.bias[col] : 0.0f;
 #pragma unroll
         for (int m = 0; m < 16; ++m)
@@ -375,9 +419,16 @@ size_t plan_tc(TcArgs& a, int k, int n) {
   a.total_units = (n + 31) / 32;
   a.ctas = a.total_units < sm_count() ? a.total_units : sm_count();
   const int per_cta = (a.total_units + a.ctas - 1) / a.ctas;
+  // Fewer units than half (a quarter) of the SMs: two (four) CTAs of a cluster share every unit along K, so that a
+  // narrow projection -- a column shard of a multi-GPU run -- still uses most of the machine.  Clusters of four
+  // one-CTA-per-SM blocks fit only 33 at a time on this part, hence the tighter bound for four.
+  a.kparts = 1;
+  if (a.total_units * 4 <= 132 && sm_count() >= 132) a.kparts = 4;
+  else if (a.total_units * 2 <= sm_count()) a.kparts = 2;
+  while (a.kparts > 1 && (k % (a.kparts * kStepK) != 0 || k / a.kparts < 4 * kStepK)) a.kparts /= 2;
   a.split = per_cta == 1 ? 4 : (per_cta == 2 ? 2 : 1);
-  while (a.split > 1 && k % (a.split * kStepK) != 0) a.split /= 2;
-  const size_t fixed = kXBufs * static_cast<size_t>(a.split) * (2 * kXHalf1 + kXRaw1) + kRedBytes + 64 * sizeof(uint64_t);
+  while (a.split > 1 && (k / a.kparts) % (a.split * kStepK) != 0) a.split /= 2;
+  const size_t fixed = kXBufs * static_cast<size_t>(a.split) * (2 * kXHalf1 + kXRaw1) + kRedBytes * a.kparts + 64 * sizeof(uint64_t);
   a.ring = static_cast<int>((220 * 1024 - fixed) / kStepBytes);
   if (a.ring > kMaxRing) a.ring = kMaxRing;
   return a.ring * static_cast<size_t>(kStepBytes) + fixed;
@@ -404,15 +455,19 @@ int launch_tc(const float* x, const float* w, const float* bias, const PeerOut& 
       if (!encode_tiled(&wmaps[u - 1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w, dims, strides, box, false)) return XDK_ERR_LAUNCH;
     }
   }
-  // x[M][K] seen as [row][k range][k inside the range]: one box brings the 64-k step of every range
-  const cuuint64_t xdims[3] = {static_cast<cuuint64_t>(k / a.split), static_cast<cuuint64_t>(a.split), static_cast<cuuint64_t>(m)};
-  const cuuint64_t xstrides[2] = {static_cast<cuuint64_t>(k / a.split) * 4, static_cast<cuuint64_t>(k) * 4};
-  const cuuint32_t xbox[3] = {kStepK, static_cast<cuuint32_t>(a.split), 16};
-  if (!encode_tiled(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, x, xdims, xstrides, xbox, false)) return XDK_ERR_LAUNCH;
+  // x[M][K] seen as [row][K part][k range][k inside the range]: one box brings the 64-k step of every range of a part
+  const int kper = k / a.kparts / a.split;
+  const cuuint64_t xdims[4] = {static_cast<cuuint64_t>(kper), static_cast<cuuint64_t>(a.split), static_cast<cuuint64_t>(a.kparts),
+                               static_cast<cuuint64_t>(m)};
+  const cuuint64_t xstrides[3] = {static_cast<cuuint64_t>(kper) * 4, static_cast<cuuint64_t>(k / a.kparts) * 4,
+                                  static_cast<cuuint64_t>(k) * 4};
+  const cuuint32_t xbox[4] = {kStepK, static_cast<cuuint32_t>(a.split), 1, 16};
+  if (!encode_tiled(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x, xdims, xstrides, xbox, false)) return XDK_ERR_LAUNCH;
   auto kernel = gemv_tc_kernel<NK>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return note_launch(err);
-  return launch(kernel, dim3(a.ctas), dim3(kThreads), smem, stream, 1u, a, wmaps[0], wmaps[1], wmaps[2], wmaps[3], xmap);
+  return launch(kernel, dim3(a.ctas, a.kparts), dim3(kThreads), smem, stream, static_cast<unsigned>(a.kparts), a, wmaps[0],
+                wmaps[1], wmaps[2], wmaps[3], xmap);
 }
 
 }  // namespace
@@ -436,7 +491,7 @@ bool gemv_tc_plan(int64_t m, int64_t k, int64_t n, bool nk, int32_t out[5]) {
   if (!gemv_tc_eligible(aligned_dummy, aligned_dummy, m, k, n, nk)) return false;
   TcArgs a;
   const size_t smem = plan_tc(a, static_cast<int>(k), static_cast<int>(n));
-  out[0] = a.ctas, out[1] = a.split, out[2] = a.ring, out[3] = static_cast<int32_t>(smem), out[4] = a.total_units;
+  out[0] = a.ctas * a.kparts, out[1] = a.split, out[2] = a.ring, out[3] = static_cast<int32_t>(smem), out[4] = a.total_units;
   return true;
 }
 

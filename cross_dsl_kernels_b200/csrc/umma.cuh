@@ -86,6 +86,50 @@ __device__ __forceinline__ void tma_box_3d(void* dst_smem, const CUtensorMap* ma
       : "memory");
 }
 
+__device__ __forceinline__ void tma_box_4d(void* dst_smem, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+          smem_u32(dst_smem)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// ---- hand-off between the CTAs of a thread-block cluster through distributed shared memory -------------------
+// Address of `local` (a shared-memory address of this CTA) in the CTA of rank `cta_rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(const void* local, unsigned cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(cta_rank));
+  return remote;
+}
+__device__ __forceinline__ void cluster_store_f4(uint32_t remote, float4 v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+// Arrive (count 1) on an mbarrier of another CTA of the cluster; orders this thread's earlier remote stores before it.
+__device__ __forceinline__ void cluster_arrive(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+// Bounded wait on an mbarrier of THIS CTA that other CTAs of the cluster arrive on (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, unsigned parity, uint64_t budget_ns = 20000000ull) {
+  const uint32_t addr = smem_u32(bar);
+  uint64_t t0 = 0;
+  for (unsigned i = 0;; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((i & 15u) == 15u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) return false;
+    }
+  }
+}
+
 // The K split of a strip of `units` 32-column units: a warp may touch only the TMEM lane quarter warp % 4, so a
 // strip narrower than 128 columns spreads S k ranges over the quarters instead (S = 4 for 1 unit, 2 for <= 2).
 __host__ __device__ inline int umma_split(int units, int k, int step_k) {

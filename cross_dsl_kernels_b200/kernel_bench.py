@@ -140,7 +140,7 @@ def bench_w4a16(m: int, k: int, n: int, group: int = 128, peak=None, replays=20,
 
 
 def bench_chain(rank: int = 0, world: int = 1, layers: int = 4, peak=None, replays=20, group=None, exchange: str = "peer",
-                dependent: bool = False, check=None) -> dict:
+                dependent: bool = False, check=None, attention: bool = False) -> dict:
     """Decode-layer chain: ``layers`` layers with distinct weights (more than L2 in total) in one
     CUDA graph; reports the per-layer median.  With world > 1 every rank must call this.
     ``check(chain, outputs_of_last_layer)`` (optional) is run on the eager result before timing."""
@@ -150,7 +150,7 @@ def bench_chain(rank: int = 0, world: int = 1, layers: int = 4, peak=None, repla
 
     cfg = ChainConfig()
     chain = DecodeLayerChain(cfg, layers=layers, rank=rank, world=world, group=group, exchange=exchange,
-                             dependent_launch=dependent)
+                             dependent_launch=dependent, attention=attention)
     if check is not None:
         out = chain.run_layers()
         torch.cuda.synchronize()
@@ -164,7 +164,11 @@ def bench_chain(rank: int = 0, world: int = 1, layers: int = 4, peak=None, repla
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
         us = float(t.item())
     nbytes = cfg.algorithmic_bytes()
-    name = f"decode_layer_chain_fp16_t{cfg.tokens}_h{cfg.hidden}_ctx{cfg.context}" + ("_pdl" if dependent else "")
+    if attention:  # K and V rows of every context position (position + 1 of them per sequence), q in, out, SwiGLU in and out
+        ctx = int((chain.positions + 1).sum())
+        nbytes += 2 * ctx * cfg.kv_heads * cfg.head_dim * 2 + 2 * cfg.tokens * cfg.hidden * 2 + 3 * cfg.tokens * cfg.mlp * 2
+    name = (f"decode_layer_chain_fp16_t{cfg.tokens}_h{cfg.hidden}_ctx{cfg.context}" + ("_attention_swiglu" if attention else "")
+            + ("_pdl" if dependent else ""))
     row = {"kernel": name, "us": round(us, 3),
            "bytes": nbytes, "gbps": round(nbytes / us * 1e-3, 1), "frac_of_8tbs": round(nbytes / us * 1e-3 / (NOMINAL_HBM_GBPS * world), 4),
            "n_gpus": world, "layers_in_graph": layers, "launches_per_layer": chain.launches_per_layer,

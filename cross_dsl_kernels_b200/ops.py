@@ -196,3 +196,61 @@ def rope_gqa_paged_kv_append(q, k, v, cos, sin, positions, page_table, sequence_
             _native.stream_ptr(q.device))
     _native.check(status, "xdk_rope_kv_append")
     return q_out
+
+
+def paged_decode_attention(q, k_cache, v_cache, positions, page_table, sequence_ids, *, page_size: int,
+                           kv_layout: str = "NHD", scale=None, context_hint: int = 0, dependent_launch: bool = False):
+    """Decode attention of one query token per sequence over the paged K/V cache that
+    :func:`rope_gqa_paged_kv_append` wrote (the token's own K/V included): FP32 softmax(scale * q.K) . V per head,
+    GQA with q_heads / kv_heads in {1, 2, 4, 8}, head_dim in {64, 128, 256}.  Not part of upstream."""
+    _gate(q)
+    dtype = q.dtype
+    _need(dtype in _RMS_DTYPES, "q must be float32, bfloat16 or float16")
+    for name, t, want in (("k_cache", k_cache, dtype), ("v_cache", v_cache, dtype), ("positions", positions, torch.int64),
+                          ("page_table", page_table, torch.int64), ("sequence_ids", sequence_ids, torch.int64)):
+        _need(t.is_cuda and t.device == q.device, f"{name} must be on the same CUDA device as q")
+        _need(t.dtype == want, f"{name} has an unexpected dtype")
+        _need(t.is_contiguous(), f"{name} must be contiguous")
+    _need(q.dim() == 3 and q.is_contiguous(), "q must be contiguous [tokens, q_heads, head_dim]")
+    _need(k_cache.dim() == 4 and k_cache.shape == v_cache.shape, "caches must be 4D paged tensors of one shape")
+    _need(positions.dim() == 1 and sequence_ids.dim() == 1 and page_table.dim() == 2, "index tensors have the wrong rank")
+    tokens, q_heads, head_dim = q.shape
+    layout = kv_layout.upper()
+    _need(layout in ("NHD", "HND"), "kv_layout must be NHD or HND")
+    _need(type(page_size) is int and page_size > 0, "page_size must be positive")
+    kv_heads = k_cache.shape[2] if layout == "NHD" else k_cache.shape[1]
+    want = (page_size, kv_heads, head_dim) if layout == "NHD" else (kv_heads, page_size, head_dim)
+    _need(tuple(k_cache.shape[1:]) == want, f"{layout} cache dimensions must be (pages, {want})")
+    _need(q_heads % kv_heads == 0 and q_heads // kv_heads in (1, 2, 4, 8), "q_heads / kv_heads must be 1, 2, 4 or 8")
+    _need(head_dim in (64, 128, 256), "head_dim must be 64, 128 or 256")
+    _need(positions.shape[0] == tokens and sequence_ids.shape[0] == tokens, "index vectors must have one entry per token")
+    scale = float(head_dim) ** -0.5 if scale is None else float(scale)
+    _need(math.isfinite(scale), "scale must be finite")
+    with torch.cuda.device(q.device):
+        out = torch.empty_like(q)
+        status = _native.lib().xdk_paged_decode_attention(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), page_table.data_ptr(),
+            sequence_ids.data_ptr(), out.data_ptr(), tokens, q_heads, kv_heads, head_dim, page_table.shape[1], page_size,
+            int(layout == "HND"), scale, int(context_hint), _native.dtype_code(dtype), _flags(dependent_launch),
+            _native.stream_ptr(q.device))
+    _native.check(status, "xdk_paged_decode_attention")
+    return out
+
+
+def swiglu(upgate, *, dependent_launch: bool = False):
+    """silu(gate) * up for a fused projection output ``[rows, 2 * width]`` laid out [up | gate]; returns [rows, width].
+    Rows may be a fixed number of elements apart (a column slice of a wider matrix).  Not part of upstream."""
+    _gate(upgate)
+    _need(upgate.dtype in _RMS_DTYPES, "upgate must be float32, bfloat16 or float16")
+    _need(upgate.dim() == 2 and upgate.shape[1] % 2 == 0 and upgate.shape[0] > 0 and upgate.shape[1] > 0,
+          "upgate must be [rows, 2 * width]")
+    _need(upgate.stride(1) == 1 and upgate.stride(0) >= upgate.shape[1], "upgate rows must be dense")
+    rows, width = upgate.shape[0], upgate.shape[1] // 2
+    with torch.cuda.device(upgate.device):
+        out = torch.empty((rows, width), dtype=upgate.dtype, device=upgate.device)
+        status = _native.lib().xdk_swiglu(upgate.data_ptr(), out.data_ptr(), rows, width,
+                                          upgate.stride(0) if rows > 1 else 2 * width, width,
+                                          _native.dtype_code(upgate.dtype), _flags(dependent_launch),
+                                          _native.stream_ptr(upgate.device))
+    _native.check(status, "xdk_swiglu")
+    return out

@@ -19,6 +19,33 @@ import torch
 from . import _native
 
 
+def exchange_handles(handle: bytes, group=None) -> list:
+    """All-gather of the ranks' 64-byte IPC handles (host side, any backend).  Raises ValueError on EVERY rank when
+    some rank contributed something that is not a 64-byte handle, so that no rank goes on to map garbage."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    handles = [None] * world
+    dist.all_gather_object(handles, handle, group=group)
+    bad = [r for r, h in enumerate(handles) if not isinstance(h, (bytes, bytearray)) or len(h) != 64]
+    if bad:
+        raise ValueError(f"ranks {bad} did not contribute a 64-byte IPC handle")
+    return [bytes(h) for h in handles]
+
+
+def agree(what: str, value, group=None) -> None:
+    """Every rank must pass the same ``value`` (arena size, carving order ...); raises ValueError on every rank
+    otherwise.  A mismatch would make ranks store into each other's arenas at different offsets."""
+    import torch.distributed as dist
+
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    values = [None] * dist.get_world_size(group)
+    dist.all_gather_object(values, value, group=group)
+    if any(v != values[0] for v in values):
+        raise ValueError(f"ranks disagree on {what}: {values}")
+
+
 class _Span:
     """Minimal ``__cuda_array_interface__`` carrier for a raw device pointer."""
 
@@ -67,10 +94,10 @@ class PeerArena:
             self.bases[self.rank] = base.value
             self._opened = []
             if self.world > 1:
+                agree("the arena size", self.nbytes, group)
                 handle = (ctypes.c_ubyte * 64)()
                 _native.check(lib.xdk_peer_export(base, handle), "xdk_peer_export")
-                handles = [None] * self.world
-                dist.all_gather_object(handles, bytes(handle), group=group)
+                handles = exchange_handles(bytes(handle), group)
                 for p, h in enumerate(handles):
                     if p == self.rank:
                         continue
@@ -102,6 +129,7 @@ class PeerArena:
         if offset + nbytes > self.nbytes:
             raise ValueError("arena exhausted")
         self._cursor = offset + ((nbytes + 255) // 256) * 256
+        agree("the carving of the arena", (offset, rows, cols, str(dtype)), self.group)
         return PeerMatrix(self, offset, rows, cols, dtype)
 
     def new_site(self) -> int:

@@ -185,7 +185,12 @@ XDK_API size_t xdk_gemv_scratch_bytes(int64_t m, int64_t k, int64_t n, int weigh
  * that device current); make that first call before starting any stream capture.  All calls share the
  * array.  It needs no clearing -- every slot a call reads was written earlier in the same call --
  * but two calls that overlap on the GPU (different streams) race on it: serialise them.
- * Results are bit-identical to xdk_gemv_f32 with split_k = 0 and a caller-provided scratch.
+ * Results are bit-identical to the tile-stream kernel of xdk_gemv_f32 (XDK_STRICT_FP32, split_k = 0, caller
+ * scratch) -- which xdk_gemv_f32 itself selects only for K*N >= 48M; below that size it runs the cluster kernels,
+ * whose summation order differs in the last bits, while this entry point runs the tile-stream kernel at every size.
+ * The per-device address cache behind this call is filled without locking: concurrent first calls from several
+ * host threads store the same value (harmless); after cudaDeviceReset() the cached address is stale -- do not
+ * reset a device this entry point has been used on.
  */
 XDK_API int xdk_gemv_f32_static_scratch(const float* x, const float* w, const float* bias, float* y,
                                         int64_t m, int64_t k, int64_t n, int weight_is_nk, void* stream);
@@ -238,6 +243,28 @@ XDK_API int xdk_w4a16(const void* x, const uint8_t* packed, const void* scales, 
               int64_t m, int64_t k, int64_t n, int group_size, void* stream);
 XDK_API int xdk_w4a16_v2(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
                  int64_t m, int64_t k, int64_t n, int group_size, unsigned flags, void* stream);
+
+/*
+ * The two ops that follow the path in a decoder layer (no counterpart in the reference, whose chain stops at
+ * the append and at the up+gate projection; expectations are this library's own FP32 restatements).
+ *
+ * xdk_paged_decode_attention: one query token per sequence against the paged K/V cache the append wrote.
+ *   out[t][h] = sum_j softmax_j(scale * q[t][h] . K[j][h / G]) * V[j][h / G],  j = 0 .. positions[t] (the token's own
+ *   K/V are in the cache already), G = q_heads / kv_heads in {1, 2, 4, 8}, head_dim in {64, 128, 256}; q and out
+ *   [tokens, q_heads, head_dim] contiguous; caches, positions, page_table, sequence_ids and the address
+ *   translation exactly as in xdk_rope_kv_append.  FP32 scores, softmax and accumulation.  context_hint: the longest
+ *   context the caller expects (bounds how finely the context is split across CTAs; <= 0: long).  One launch, no
+ *   scratch: the slices of a (token, KV head) are merged through distributed shared memory in a fixed order.
+ * xdk_swiglu: out[r][j] = silu(upgate[r][width + j]) * upgate[r][j] for j < width -- columns [0, width) of the fused
+ *   projection are "up", [width, 2 width) "gate"; in_ld / out_ld: elements between rows.
+ */
+XDK_API int xdk_paged_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions,
+                               const int64_t* page_table, const int64_t* sequence_ids, void* out, int64_t tokens,
+                               int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t max_pages_per_seq,
+                               int64_t page_size, int cache_is_hnd, float scale, int64_t context_hint, int dtype,
+                               unsigned flags, void* stream);
+XDK_API int xdk_swiglu(const void* upgate, void* out, int64_t rows, int64_t width, int64_t in_ld, int64_t out_ld, int dtype,
+               unsigned flags, void* stream);
 
 /*
  * Symmetric INT4 quantisation on the device, into the format xdk_w4a16 reads: weight [n, k] row-major of

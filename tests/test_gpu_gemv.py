@@ -111,6 +111,10 @@ def test_tile_stream_path(layout, m, k, n):
     (16, 8192, 6148),
     (16, 1024, 4096),    # the smallest matrix the path takes
     (16, 4096, 28672),
+    (16, 4096, 1792),    # fewer units than half the SMs (a column shard): K also split over a cluster of two CTAs
+    (12, 8192, 2048),
+    (16, 4096, 1024),    # ... and over a cluster of four
+    (7, 16384, 1000),    # ragged last unit with the cluster split
 ])
 def test_tensor_core_path(layout, m, k, n):
     """The default for 4 < M <= 16 and K % 64 == 0: tcgen05 kind::tf32 MMAs on operands split into two

@@ -84,3 +84,64 @@ def test_replay_count_without_a_process_group():
     from cross_dsl_kernels_b200.timing import lockstep_replays
     assert lockstep_replays(10.0, 20, device="cpu") == 2000
     assert lockstep_replays(1e6, 2, device="cpu") == 1
+
+
+# ---- host side of the peer-mapped path: agreement checks and failures made on the host (no GPU involved)
+
+
+def _peer_host_worker(rank: int, world: int, port: int, ok):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        from cross_dsl_kernels_b200.peer import agree, exchange_handles
+        # 1. well-formed handles come back rank-major on every rank
+        handles = exchange_handles(bytes([rank]) * 64)
+        assert handles == [bytes([r]) * 64 for r in range(world)]
+        # 2. a rank that contributes a truncated handle (a dropped or mangled message) makes EVERY rank refuse
+        try:
+            exchange_handles(bytes([rank]) * (64 if rank == 0 else 10))
+            raise AssertionError("a 10-byte handle was accepted")
+        except ValueError as err:
+            assert "ranks [1]" in str(err)
+        # 3. ranks that disagree on the arena size or the carving are stopped before any kernel runs
+        agree("a value all ranks share", 4096)
+        try:
+            agree("the arena size", 4096 + rank)
+            raise AssertionError("a size mismatch was accepted")
+        except ValueError:
+            pass
+        ok[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_arena_host_agreement_with_two_gloo_ranks():
+    world = 2
+    ok = mp.get_context("spawn").Array("i", [0] * world)
+    mp.spawn(_peer_host_worker, args=(world, _free_port(), ok), nprocs=world, join=True)
+    assert list(ok) == [1] * world
+
+
+def _leaver_worker(rank: int, world: int, port: int, ok):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    from cross_dsl_kernels_b200.peer import agree
+    agree("the first step", 1)
+    if rank == 1:
+        ok[rank] = 1
+        return  # leaves between steps without joining the next exchange (a rank that died on the host)
+    try:
+        agree("the step the other rank never joins", 2)
+    except Exception:  # the short process-group timeout turns the missing rank into an error, not a hang
+        ok[rank] = 1
+
+
+def test_a_rank_that_leaves_is_an_error_not_a_hang():
+    world = 2
+    ok = mp.get_context("spawn").Array("i", [0] * world)
+    mp.spawn(_leaver_worker, args=(world, _free_port(), ok), nprocs=world, join=True)
+    assert list(ok) == [1] * world

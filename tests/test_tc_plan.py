@@ -66,3 +66,16 @@ def test_headline_shapes():
     assert plan(16, 4096, 14336)[1][:3] == [148, 1, 5]
     assert plan(16, 4096, 4096)[1][:3] == [128, 4, 3]
     assert plan(16, 4096, 6144, 1)[1][:3] == [148, 2, 5]
+
+
+@pytest.mark.parametrize("k,n,parts", [(4096, 1792, 2), (4096, 2368, 2), (4096, 1024, 4), (8192, 1056, 4), (4096, 2400, 1),
+                                       (256, 16384, 1)])
+def test_narrow_projections_split_k_over_a_cluster(k, n, parts):
+    """Fewer 32-column units than half (a quarter) of the SMs: two (four) CTAs share every unit along K, so the
+    plan reports parts x units CTAs."""
+    took, (ctas, split, ring, smem, units) = plan(16, k, n, 0)
+    assert took == 1
+    assert units == -(-n // 32)
+    assert ctas == min(SMS, units) * parts
+    assert (k // parts) % (64 * split) == 0
+    assert smem <= MAX_DYNAMIC_SMEM

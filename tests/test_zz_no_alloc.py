@@ -54,6 +54,28 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(nk):
         assert float((got.double() - reference).abs().max()) <= 4e-4  # the projection's own gate at K = 4096
 
 
+@pytest.mark.parametrize("nk", [False, True])
+def test_static_scratch_on_a_small_matrix_runs_the_tile_stream_kernel_too(nk):
+    """Below K*N = 48M xdk_gemv_f32 itself would pick the cluster kernels (another summation order); the
+    allocation-free entry point runs the tile-stream kernel at every size.  So on a small matrix it is held to the
+    projection's gate against an FP64 product, and to giving the same bits twice -- not to equality with xdk_gemv_f32."""
+    m, k, n = 9, 1024, 640
+    g = torch.Generator().manual_seed(22)
+    w = (torch.randn(n, k, generator=g) / 32 if nk else torch.randn(k, n, generator=g) / 32).cuda()
+    b = (0.02 * torch.randn(n, generator=g)).cuda()
+    x = torch.randn(m, k, generator=g).cuda()
+    reference = x.double() @ (w.double().t() if nk else w.double()) + b.double()
+    results = []
+    for _ in range(2):
+        got = torch.full((m, n), float("nan"), device="cuda")
+        _project("static", x, w, b, got, nk)
+        torch.cuda.synchronize()
+        assert float((got.double() - reference).abs().max()) <= 2e-4
+        assert float((got.double() - reference).norm() / reference.norm()) <= 1e-5
+        results.append(got)
+    assert torch.equal(results[0], results[1])
+
+
 def test_static_scratch_rejects_what_it_cannot_hold():
     from cross_dsl_kernels_b200 import _native
     lib = _native.lib()
