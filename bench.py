@@ -294,6 +294,33 @@ def w4a16_row(kb, m, n, peak, dependent=False):
     return row
 
 
+def attention_row(kb, context, peak, dependent=False):
+    from oracle import attention as oracle_attention
+
+    def check(stage, out):
+        got, q, kc, vc, positions, table, ids = out
+        flat = table.reshape(-1)
+        compact = torch.arange(flat.numel(), dtype=torch.int64).reshape(table.shape)  # the call's pages, renumbered
+        want = oracle_attention.paged_decode_attention(q.cpu(), kc[flat].cpu(), vc[flat].cpu(), positions.cpu(), compact, ids.cpu(),
+                                                       page_size=kc.shape[1])
+        _need(bool(torch.isfinite(got).all()), f"attention ctx{context} {stage}: non-finite output")
+        _need(_rel_l2(got.cpu().float(), want.float()) <= 2e-3, f"attention ctx{context} {stage}: rel-L2")
+
+    row = kb.bench_attention(context, peak=peak, check=check, dependent=dependent)
+    row["parity"] = "unpinned (no upstream counterpart; FP32 restatement)"
+    return row
+
+
+def swiglu_row(kb, rows, width, peak, dependent=False):
+    from oracle import attention as oracle_attention
+
+    def check(stage, out):
+        got, upgate = out
+        _need(_ulps16(got.cpu(), oracle_attention.swiglu(upgate.cpu())) <= 1, f"swiglu {stage}: more than one ulp off")
+
+    return kb.bench_swiglu(rows, width, peak=peak, check=check, dependent=dependent)
+
+
 def gated_table(kb, peak: float) -> list[dict]:
     rows = [kb.bench_noop(), kb.bench_noop(dependent=True)]
     for dtype in (torch.float32, torch.bfloat16):
@@ -316,6 +343,9 @@ def gated_table(kb, peak: float) -> list[dict]:
         for m in (1, 16):
             rows.append(w4a16_row(kb, m, n, peak))
             rows.append(w4a16_row(kb, m, n, peak, dependent=True))
+    for context in (1024, 8192):  # the two ops that follow the path in a decode layer (not part of upstream)
+        rows.append(attention_row(kb, context, peak))
+    rows.append(swiglu_row(kb, 16, 14336, peak))
     cores = torch.get_num_threads()
     for row in rows:
         if "cpu_us" in row:

@@ -34,7 +34,7 @@ unsigned w4a16_fault_word();
 
 // tcgen05 FP32 projection (gemv_tc.cu): whether it takes the shape, and its launch
 bool gemv_tc_eligible(const float* x, const float* w, int64_t m, int64_t k, int64_t n, bool nk);
-bool gemv_tc_plan(int64_t m, int64_t k, int64_t n, bool nk, int32_t out[5]);  // {CTAs, K split, ring depth, smem bytes, units}
+int gemv_tc_plan(int64_t m, int64_t k, int64_t n, bool nk, int32_t out[5]);  // {CTAs, lane-quarter K split, ring depth, smem bytes, units}; returns the cluster size, 0 = declined
 
 // Flags of the *_v2 entry point that is executing on this host thread (0 outside one).
 unsigned call_flags();

@@ -692,7 +692,7 @@ unsigned gemv_fault_word() {
 
 extern "C" int xdk_gemv_tc_plan(int64_t m, int64_t k, int64_t n, int weight_is_nk, int32_t* out5) {
   if (!out5) return XDK_ERR_ARG;
-  return xdk::gemv_tc_plan(m, k, n, weight_is_nk != 0, out5) ? 1 : 0;
+  return xdk::gemv_tc_plan(m, k, n, weight_is_nk != 0, out5);
 }
 
 extern "C" size_t xdk_gemv_scratch_bytes(int64_t m, int64_t k, int64_t n, int weight_is_nk) {

@@ -4,39 +4,42 @@
 // (16 rows of x against every weight), not by HBM; the tensor cores have the throughput, but a TF32 product keeps
 // only 11 significant bits of each operand.  So every operand is split into two TF32 numbers,
 //     v = hi + lo,   hi = v with the low 13 mantissa bits cleared,   lo = v - hi  (exact in FP32),
-// and the product is formed as hi.hi + hi.lo + lo.hi -- three MMAs per k block, FP32 accumulation in TMEM.  The
-// dropped lo.lo term and the bits of lo the tensor core ignores are below 2^-21 relative per product.  The
-// accumulation inside the tensor core may truncate instead of rounding; to keep that bias small the sum is spread
-// over up to sixteen accumulators per k range that are added in FP32 in a fixed order at the end, so results are
-// deterministic.  Measured against an FP64 product the relative L2 error is ~1e-6, inside the 1e-5 gate of the
-// projection; callers that need strict FP32 FMA arithmetic pass scratch to xdk_gemv_f32 and get the CUDA-core
-// tile-stream kernel instead.
+// and the product is formed as hi.hi + hi.lo + lo.hi with FP32 accumulation in TMEM.  The dropped lo.lo term and
+// the bits of lo the tensor core ignores are below 2^-21 relative per product.  The accumulation inside the
+// tensor core may truncate instead of rounding; to keep that bias small the sum is spread over several
+// accumulators (one or more per MMA issuer, the hi.lo products in columns of their own) that are added in FP32 in a
+// fixed order at the end, so results are deterministic.  Measured against an FP64 product the relative L2 error
+// stays inside the 1e-5 gate of the projection up to K = 16384; callers that need strict FP32 FMA arithmetic pass
+// XDK_STRICT_FP32 and get the CUDA-core kernels instead.
 //
 // Layout of the work (same scheme as the W4A16 tcgen05 kernel): operands are swapped so that the UMMA "M"
-// dimension (128 TMEM lanes) carries output columns, D[128 lanes x 16 S] += A[128 x 8 k] * B[8 k x 16 S], A = W (split)
-// in tensor memory, B = x^T (split) in shared memory.  One persistent CTA per SM owns an evenly dealt range of
-// 32-column units and walks it in strips of <= 4 units, full K each; narrow strips split K S ways over the TMEM
-// lane quarters and add the S partial sums through shared memory in a fixed order; S is one value per launch
-// (4 when no CTA has more than one unit, 2 for two, else 1), which also sizes the x buffers, and whatever shared
-// memory they leave goes to the W ring.  A projection with fewer units than half the SMs (a column shard of a
-// multi-GPU run) is additionally split along K over the 2 or 4 CTAs of a thread-block cluster: every CTA of the
-// cluster walks the same strips over its own part of K, the parts store their partial sums into the rank-0 CTA's
-// shared memory (distributed shared memory, mbarrier hand-off with bounded waits) and rank 0 adds them in rank
-// order, so the result stays deterministic.
+// dimension (128 TMEM lanes) carries output columns, A = W (split) in tensor memory, B = x^T (split) in shared
+// memory.  The hi and lo images of x sit one after the other at the same row-group pitch, so one operand
+// descriptor covers [x_hi | x_lo] and a k block takes two MMAs instead of three:
+//     D[128 lanes x 32 S] += W_hi[128 x 8 k] * [x_hi | x_lo][8 k x 32 S]      (hi.hi and hi.lo, side by side)
+//     D[128 lanes x 16 S] += W_lo[128 x 8 k] * x_hi[8 k x 16 S]               (lo.hi, onto the hi.hi columns)
+// and the epilogue adds the two halves.  One persistent CTA per SM owns an evenly dealt range of 32-column units
+// and walks it in strips of <= 4 units.  K can be split two ways: S ways over the TMEM lane quarters of a CTA
+// (narrow strips; the S partial sums meet in shared memory) and over the 2, 4 or 8 CTAs of a thread-block cluster
+// (every CTA walks the same strips over its own part of K, the parts store their partial sums into the rank-0
+// CTA's shared memory -- distributed shared memory, mbarrier hand-off with bounded waits -- and rank 0 adds them
+// in rank order); plan_tc weighs the combinations.  Sums are added in a fixed order everywhere: deterministic.
 //   TMA warps (4)      : one lane each, one warp per TMEM lane quarter: the W tile of a 64-k step (NK: two 128-byte
 //                        swizzled [32 columns][32 k] boxes per quarter; KN: one [64 k][32 u columns] box per k range,
-//                        u = units of the strip, so that HBM sees runs of up to 512 bytes) into a ring of step buffers.  Four warps because a warp gets a TMA box copy out only every ~230
-//                        cycles: one producer issuing all boxes of a step was the bottleneck (NK slower than KN)
-//   x warps (2)        : one lane issues one TMA box per k range ([16 rows][64 k]); both warps split every 16-byte
-//                        unit into hi and lo and move it to its place in the two K-major core-matrix operand images
+//                        u = units of the strip, so that HBM sees runs of up to 512 bytes) into a ring of step buffers
+//   x warps (2)        : one lane issues one TMA box per step ([16 rows][S k ranges][64 k]); both warps split every
+//                        16-byte unit into hi and lo and move it to its place in the two K-major core-matrix images
 //   split warps (8)    : thread = one TMEM lane = one output column; warp w owns lane quarter w % 4 and k half
 //                        w / 4 of every step: shared loads -> hi/lo -> tcgen05.st into the stage's hi and lo columns
-//   MMA warps (4)      : one lane each.  A warp gets a tcgen05.mma out only every ~118 cycles whatever the shape,
-//                        but warps issue side by side (measured: 8 warps, one MMA per 15 cycles in aggregate), so
-//                        the 8 k blocks of a step are dealt round-robin to 4 issuers (3 MMAs per block), each with
-//                        its own accumulators
+//   MMA warps (4)      : one lane each; the 8 k blocks of a step are dealt round-robin to the 4 issuers (a warp gets
+//                        a tcgen05.mma out only every ~118 cycles, but warps issue side by side), each with its
+//                        own accumulators
 //   split warps 0-3    : epilogue -- tcgen05.ld of the accumulators, fixed-order sum, bias, FP32 store
-// TMEM columns (512): (256 / issuers) i + 16 S a .. accumulator a of issuer i, 256 + 128 s .. stage s (64 hi columns, 64 lo).
+// A step is a chain split -> MMA -> (stage free) -> split with ~0.1-0.2 us of mbarrier / tcgen05.commit latency per
+// link; with two A stages that chain, not HBM, set the step time (a run without any W traffic took as long).
+// Hence three stages whenever the accumulators fit beside them, and three x buffers.
+// TMEM columns (512): accumulators first -- (512 - 128 stages) / 4 per issuer, 32 S (two-MMA form) per accumulator
+// -- then stage s at 128 s: 64 hi columns, 64 lo.
 // Every wait is time-bounded; on a timeout the kernel raises a fault word, stops issuing work, and still frees
 // its TMEM columns before it returns.
 #include <cuda_runtime.h>
@@ -52,23 +55,27 @@ namespace {
 __device__ unsigned int g_tc_fault;  // set when a bounded wait gives up
 
 constexpr int kStepK = 64;                      // k per step
-constexpr int kMaxK = 16384;                    // largest K the split-TF32 accumulation keeps inside the 1e-5 gate
+constexpr int kMaxK = 16384;                    // largest K the path takes
+// The tensor core's accumulation truncates, so the error of a sum grows with the number of products one accumulator
+// adds: measured against FP64 with the eight accumulators a CTA has, zero-mean operands give a relative L2 error of
+// 2.9e-6 at 4096 k per CTA and 1.0e-5 at 16384; all-positive operands (the worst case) 7.6e-6 and 3.0e-5.  A CTA
+// therefore never sums more than 4096 k: longer rows are split over the CTAs of a cluster (whose partial sums are
+// added in FP32 with rounding) or, when K does not divide, left to the FP32-FMA kernels.
+constexpr int kMaxKPerCta = 4096;
 constexpr int kMaxRing = 8;                     // W step buffers: as many as shared memory leaves (plan.ring)
 constexpr int kQuarterBytes = 32 * kStepK * 4;  // one lane quarter's tile: 32 columns x 64 k
 constexpr int kStepBytes = 4 * kQuarterBytes;
-constexpr int kStages = 2;                      // A stages in TMEM
+constexpr int kStages = 2;                      // A stages in TMEM (a third one measured no faster)
 constexpr int kStageCols = 2 * kStepK;          // hi columns then lo columns
 constexpr int kMaxIssuers = 4;
-constexpr int kAccRegion = 256;                 // TMEM columns for accumulators: 256 / issuers each, 16 S per accumulator
-constexpr int kTmemCols = 512;
-constexpr int kTmemA = kAccRegion;
-static_assert(kTmemA + kStages * kStageCols <= kTmemCols, "stages must fit the TMEM allocation");
+constexpr int kTmemCols = 512;                  // accumulators first (256 columns, 64 per issuer), then the stages
+constexpr int kTmemA = kTmemCols - kStages * kStageCols;
 constexpr int kXLbo = 128, kXSbo = (kStepK / 4) * kXLbo;  // x image: [row group of 8][16 k groups][8 rows x 16 B]
 constexpr int kXHalf1 = 2 * kXSbo;              // hi (or lo) image of one k range: 16 rows
 constexpr int kXRaw1 = 16 * kStepK * 4;         // one k range of [16 rows][64 k] as TMA lands it
-constexpr int kXBufs = 2;
+constexpr int kXBufs = kStages;                 // x steps in flight: buffer s serves A stage s, one barrier frees both
 constexpr int kRedBytes = 128 * 16 * 4;         // k-range partials: [lane][16] floats
-constexpr int kMaxParts = 4;                    // CTAs of a cluster sharing a strip along K
+constexpr int kMaxParts = 8;                    // CTAs of a cluster sharing a strip along K (portable cluster size)
 constexpr int kWTma = 8, kWX0 = 12, kWMma0 = 14;  // warp roles; 0-7 split, 8-11 TMA, 12-13 x, 14-17 MMA
 constexpr int kThreads = (kWMma0 + kMaxIssuers) * 32;
 constexpr uint32_t kHiMask = 0xffffe000u;       // keeps sign, exponent and the 10 mantissa bits TF32 uses
@@ -80,8 +87,42 @@ struct TcArgs {
   int ctas, total_units;
   int split;  // k ranges per strip (1, 2, 4), the same for every strip of the launch
   int ring;   // W step buffers
-  int kparts; // CTAs of a cluster that share every strip, each walking K / kparts (1, 2, 4); grid = (ctas, kparts)
+  int kparts; // CTAs of a cluster that share every strip, each walking K / kparts (1, 2, 4, 8); grid = (ctas, kparts)
+  int wide;   // 1: W_hi meets [x_hi | x_lo] in one MMA of 32 S columns (2 MMAs per k block); 0: three MMAs of 16 S
+  int max_accs;
+  int rotate;     // 1: every CTA starts its k loop at another step (no two CTAs ask L2 for the same x lines at once)
+  int tight_ring; // 1: a CTA whose strips are narrower than 128 columns cuts the ring into smaller, more slots
 };
+
+// Position in a ring of `depth` buffers guarded by full/empty mbarriers: the slot and the parity a consumer waits
+// for on the slot's "full" barrier; a producer waits for parity ^ 1 on the "empty" barrier (which a fresh barrier
+// already satisfies).  Kept by increments: the roles' loops are latency chains, a division per step shows.
+struct RingPos {
+  int slot = 0;
+  uint32_t parity = 0;
+  __device__ __forceinline__ void advance(int depth) {
+    if (++slot == depth) slot = 0, parity ^= 1u;
+  }
+};
+
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {  // no wait: see tmem_ld_wait16
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+// Waits for every tcgen05.ld of this thread; the registers pass through the statement so that no use of them can
+// be scheduled before the wait.
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :: "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 
 __device__ __forceinline__ void split_tf32(uint32_t v, uint32_t& hi, uint32_t& lo) {
   hi = v & kHiMask;
@@ -94,24 +135,25 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
                const __grid_constant__ CUtensorMap wmap3, const __grid_constant__ CUtensorMap wmap4,
                const __grid_constant__ CUtensorMap xmap) {  // wmap2-4 (KN only): boxes 64, 96, 128 columns wide
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  const int S = a.split, kRing = a.ring;
-  const int issuers = kMaxIssuers, acc_cols = kAccRegion / issuers;
+  const int S = a.split;
+  const int issuers = kMaxIssuers, acc_cols = kTmemA / issuers;
+  const int acc_w = a.wide ? 32 : 16;  // columns of an accumulator per k range: [hi.hi + lo.hi | hi.lo] or one sum
   const int kXHalfBytes = S * kXHalf1, kXBytes = 2 * kXHalfBytes, kXRawBytes = S * kXRaw1;
-  unsigned char* ring = smem_raw;                            // [ring][kStepBytes]
-  unsigned char* xbuf = ring + kRing * kStepBytes;           // [kXBufs][hi image | lo image], 16 S rows each
+  unsigned char* ring = smem_raw;                            // [a.ring][kStepBytes], re-cut below
+  unsigned char* xbuf = ring + a.ring * kStepBytes;          // [kXBufs][hi image | lo image], 16 S rows each
   unsigned char* xraw = xbuf + kXBufs * kXBytes;             // [kXBufs][16 rows][S k ranges][64 k]
-  float* red = reinterpret_cast<float*>(xraw + kXBufs * kXRawBytes);
-  // partial sums of the other CTAs of the cluster land here (in the rank-0 CTA): [part - 1][lane][16] floats
-  float* inbox = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(red) + kRedBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(inbox) + (a.kparts - 1) * kRedBytes);
+  // k-range partials of this CTA, [row quad][lane] float4 (a thread's 16 sums sit 2 KB apart: conflict-free)
+  float4* red = reinterpret_cast<float4*>(xraw + kXBufs * kXRawBytes);
+  // partial sums of the other CTAs of the cluster land here (in the rank-0 CTA): [part - 1][row quad][lane] float4
+  float4* inbox = red + kRedBytes / sizeof(float4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(inbox + (a.kparts - 1) * (kRedBytes / sizeof(float4)));
   uint64_t* w_full = bars;                 // [kMaxRing] TMA bytes of a W step landed
   uint64_t* w_empty = w_full + kMaxRing;   // [kMaxRing] the 8 split warps are done with the step
   uint64_t* a_full = w_empty + kMaxRing;   // [kStages] the 8 split warps wrote the stage to TMEM
-  uint64_t* a_empty = a_full + kStages;    // [kStages] every issuer's MMAs that read the stage completed
-  uint64_t* x_raw = a_empty + kStages;     // [kXBufs]  TMA bytes of an x step landed
+  uint64_t* mma_done = a_full + kStages;   // [kStages] every issuer's MMAs on the stage (and its x images) completed
+  uint64_t* x_raw = mma_done + kStages;    // [kXBufs]  TMA bytes of an x step landed
   uint64_t* x_full = x_raw + kXBufs;       // [kXBufs]  the x warps wrote both operand images
-  uint64_t* x_empty = x_full + kXBufs;     // [kXBufs]  every issuer's MMAs that read the images completed
-  uint64_t* acc_full = x_empty + kXBufs;   // [1]
+  uint64_t* acc_full = x_full + kXBufs;    // [1]
   uint64_t* inbox_full = acc_full + 1;     // [1] rank 0: the other parts stored a strip's partials (128 arrivals each)
   uint64_t* inbox_free = inbox_full + 1;   // [1] other ranks: rank 0 has read the partials of the previous strip
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(inbox_free + 1);
@@ -123,110 +165,143 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
   const int k_len = a.k / a.kparts, k_base = part * k_len;
   UmmaCursor cur;
   cur.init(blockIdx.x, a.ctas, a.total_units, k_len, kStepK, S);
+  // The ring holds a.ring steps of 128 columns.  A CTA whose widest strip (its first) has fewer columns needs less
+  // per step and cuts the same bytes into more slots: more W in flight against the 3-4 us a load takes under load.
+  const int widest = min(4, cur.unit_end - cur.unit);
+  const int slot_bytes = (a.tight_ring && S == 1 && widest > 0) ? widest * kQuarterBytes : kStepBytes;
+  const int kRing = min(kMaxRing, a.ring * kStepBytes / slot_bytes);
+  // first k step of this CTA's loop over a strip (taken modulo the strip's steps)
+  const int rot_seed = a.rotate ? static_cast<int>(blockIdx.x) * 5 + part * 3 : 0;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kRing; ++i) {
-      mbar_init(w_full + i, 4);   // one arrival (with its bytes) per TMA warp
-      mbar_init(w_empty + i, 8);
+  if (warp == 0) {  // one barrier per lane
+    if (lane < kRing) {
+      mbar_init(w_full + lane, 4);   // one arrival (with its bytes) per TMA warp
+      mbar_init(w_empty + lane, 8);
     }
-    for (int i = 0; i < kXBufs; ++i) {
-      mbar_init(x_raw + i, 1);
-      mbar_init(x_full + i, 1);
-      mbar_init(x_empty + i, issuers);
+    if (lane < kStages) {
+      mbar_init(x_raw + lane, 1);
+      mbar_init(x_full + lane, 1);
+      mbar_init(a_full + lane, 8);
+      mbar_init(mma_done + lane, issuers);
     }
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(a_full + i, 8);
-      mbar_init(a_empty + i, issuers);
+    if (lane == 0) {
+      mbar_init(acc_full, issuers);
+      mbar_init(inbox_full, 128 * (a.kparts - 1) > 0 ? 128 * (a.kparts - 1) : 1);
+      mbar_init(inbox_free, 1);
     }
-    mbar_init(acc_full, issuers);
-    mbar_init(inbox_full, 128 * (a.kparts - 1) > 0 ? 128 * (a.kparts - 1) : 1);
-    mbar_init(inbox_free, 1);
     mbar_fence_init();
+  } else if (warp >= kWTma && warp < kWX0 && lane == 0) {
+    prefetch_tensormap(warp == kWTma ? &wmap : (warp == kWTma + 1 ? &wmap2 : (warp == kWTma + 2 ? &wmap3 : &wmap4)));
+  } else if (warp == kWX0 && lane == 0) {
+    prefetch_tensormap(&xmap);
   }
-  if (warp == kWTma) tmem_alloc<kTmemCols>(tmem_slot);
-  tc_fence_before();
-  __syncthreads();
-  if (a.kparts > 1) {  // every CTA's barriers exist before a peer may arrive on them
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  __syncthreads();  // the barriers exist: the TMA and x warps start their loads
+  // Every CTA of a cluster must know that its peers' barriers exist before it arrives on them (the first remote
+  // access is in the epilogue).  Everybody arrives here; each warp waits where it has nothing better to do.
+  const bool clustered = a.kparts > 1;
+  if (clustered) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  uint32_t tmem_base = 0;
+  if (warp < kWTma || warp >= kWMma0) {  // the warps that touch tensor memory: split warps and MMA warps
+    if (warp == kWMma0) tmem_alloc<kTmemCols>(tmem_slot);
+    tc_fence_before();
+    asm volatile("bar.sync 4, %0;" ::"n"((kWTma + kMaxIssuers) * 32) : "memory");
+    tc_fence_after();
+    tmem_base = *tmem_slot;
+    if (clustered) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
 
   if (warp >= kWTma && warp < kWX0) {
     // ------------------------------------------------------------ TMA producers: W tiles, one lane quarter each
-    if (lane == 0) {
+    {  // the whole warp runs the loop (waits included), one elected lane issues
       const int lq = warp - kWTma;
       bool ok = true;
+      RingPos w;
       while (ok && cur.begin_strip()) {
         const int qpk = 4 / cur.split;  // lane quarters per k range = units the strip can hold
         const bool live = lq % qpk < cur.units;
         const int col0 = (cur.unit + lq % qpk) * 32, k_range0 = (lq / qpk) * cur.kper;
+        int kk = rot_seed % cur.steps;  // the step this CTA walks now: kk, kk + 1, ..., steps - 1, 0, ...
         do {
-          const int buf = cur.q % kRing;
-          if (cur.q >= kRing && !mbar_wait(w_empty + buf, ((cur.q / kRing) - 1) & 1)) {
-            ok = false;
-            break;
-          }
-          const int k0 = k_base + k_range0 + cur.kc * kStepK;
-          if (NK) {  // two [32 columns][32 k] boxes, 128-byte rows, swizzled
-            if (!live) {
-              mbar_arrive_cta(w_full + buf);
-              continue;
+          const int buf = w.slot;
+          ok = __all_sync(0xffffffffu, mbar_wait(w_empty + buf, w.parity ^ 1u));
+          if (!ok) break;
+          w.advance(kRing);
+          const int k0 = k_base + k_range0 + kk * kStepK;
+          kk = kk + 1 == cur.steps ? 0 : kk + 1;
+          if (elect_one()) {
+            unsigned char* dst = ring + buf * slot_bytes + lq * kQuarterBytes;
+            if (NK) {  // two [32 columns][32 k] boxes, 128-byte rows, swizzled
+              if (!live) {
+                mbar_arrive_cta(w_full + buf);
+              } else {
+                mbar_expect_tx(w_full + buf, static_cast<unsigned>(kQuarterBytes));
+                tma_box_2d(dst, &wmap, k0, col0, w_full + buf);
+                tma_box_2d(dst + kQuarterBytes / 2, &wmap, k0 + 32, col0, w_full + buf);
+              }
+            } else {   // the first quarter of each k range fetches [64 k][32 u columns] for all its quarters
+              if (lq % qpk != 0) {
+                mbar_arrive_cta(w_full + buf);
+              } else {
+                mbar_expect_tx(w_full + buf, static_cast<unsigned>(cur.units * kQuarterBytes));
+                const CUtensorMap* map = cur.units == 1 ? &wmap : (cur.units == 2 ? &wmap2 : (cur.units == 3 ? &wmap3 : &wmap4));
+                tma_box_2d(dst, map, col0, k0, w_full + buf);
+              }
             }
-            mbar_expect_tx(w_full + buf, static_cast<unsigned>(kQuarterBytes));
-            unsigned char* dst = ring + buf * kStepBytes + lq * kQuarterBytes;
-            tma_box_2d(dst, &wmap, k0, col0, w_full + buf);
-            tma_box_2d(dst + kQuarterBytes / 2, &wmap, k0 + 32, col0, w_full + buf);
-          } else {   // the first quarter of each k range fetches [64 k][32 u columns] for all its quarters
-            if (lq % qpk != 0) {
-              mbar_arrive_cta(w_full + buf);
-              continue;
-            }
-            mbar_expect_tx(w_full + buf, static_cast<unsigned>(cur.units * kQuarterBytes));
-            unsigned char* dst = ring + buf * kStepBytes + lq * kQuarterBytes;
-            const CUtensorMap* map = cur.units == 1 ? &wmap : (cur.units == 2 ? &wmap2 : (cur.units == 3 ? &wmap3 : &wmap4));
-            tma_box_2d(dst, map, col0, k0, w_full + buf);
           }
+          __syncwarp();
         } while (cur.next_step());
       }
-      if (!ok) atomicOr(&g_tc_fault, 1u);
+      if (!ok && lane == 0) atomicOr(&g_tc_fault, 1u);
     }
+    if (clustered) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   } else if (warp >= kWMma0) {
     // ------------------------------------------------------------ MMA issuers
-    if (lane == 0 && warp - kWMma0 < issuers) {
+    if (warp - kWMma0 < issuers) {  // the whole warp runs the loop; one elected lane issues
       const int issuer = warp - kWMma0;
       const uint64_t xd0 = umma_desc(smem_u32(xbuf), kXLbo, kXSbo);
       const uint32_t xd_lo = static_cast<uint32_t>(xd0), xd_hi = static_cast<uint32_t>(xd0 >> 32);
       bool ok = true;
+      RingPos st;
       while (ok && cur.begin_strip()) {
-        const uint32_t idesc = umma_idesc(16 * cur.split, 2u);
-        const int naccs = min(acc_cols / (16 * S), cur.steps);
+        const uint32_t idesc = umma_idesc(16 * cur.split, 2u), idesc_wide = umma_idesc(32 * cur.split, 2u);
+        const int naccs = min(min(acc_cols / (acc_w * S), cur.steps), a.max_accs);
         do {
-          const int xb = cur.q % kXBufs, s = cur.q % kStages;
-          ok = mbar_wait(x_full + xb, (cur.q / kXBufs) & 1) && mbar_wait(a_full + s, (cur.q / kStages) & 1);
+          const int s = st.slot, xb = s;
+          ok = __all_sync(0xffffffffu, mbar_wait(x_full + xb, st.parity) && mbar_wait(a_full + s, st.parity));
           if (!ok) break;
+          st.advance(kStages);
           tc_fence_after();
-          const int sel = cur.kc % naccs;
-          const uint32_t acc = tmem_base + issuer * acc_cols + sel * 16 * S;
+          // All MMAs of a step go to one accumulator, steps rotate over the accumulators: measured, an issuer that
+          // changes accumulator from one MMA to the next loses 50-80 cycles per MMA.
+          const int nj = kStepK / 8 / issuers;  // k blocks of this issuer per step: issuer, issuer + issuers, ...
+          const uint32_t acc = tmem_base + issuer * acc_cols + (cur.kc % naccs) * acc_w * S;
           const bool fresh = cur.kc < naccs;  // first step that touches this accumulator in the strip
           const uint32_t a_hi = tmem_base + kTmemA + s * kStageCols + issuer * 8;
           const uint32_t x_lo = xd_lo + ((xb * kXBytes + issuer * 2 * kXLbo) >> 4);
-          for (int j = 0; j * issuers < kStepK / 8; ++j) {  // k blocks issuer, issuer + issuers
+          if (elect_one()) {
+          for (int j = 0; j < nj; ++j) {
             uint64_t b_hi, b_lo;
             const uint32_t off = (j * issuers * 2 * kXLbo) >> 4;
             asm("mov.b64 %0, {%1, %2};" : "=l"(b_hi) : "r"(x_lo + off), "r"(xd_hi));
             asm("mov.b64 %0, {%1, %2};" : "=l"(b_lo) : "r"(x_lo + off + (kXHalfBytes >> 4)), "r"(xd_hi));
             const uint32_t ah = a_hi + j * issuers * 8;
-            umma_tf32_ta(acc, ah, b_hi, idesc, !(fresh && j == 0));
-            umma_tf32_ta(acc, ah, b_lo, idesc, true);
-            umma_tf32_ta(acc, ah + kStepK, b_hi, idesc, true);
+            if (a.wide) {  // the lo image follows the hi image at the same row-group pitch: one operand of 32 S rows
+              umma_tf32_ta(acc, ah, b_hi, idesc_wide, !(fresh && j == 0));
+              umma_tf32_ta(acc, ah + kStepK, b_hi, idesc, true);
+            } else {
+              umma_tf32_ta(acc, ah, b_hi, idesc, !(fresh && j == 0));
+              umma_tf32_ta(acc, ah, b_lo, idesc, true);
+              umma_tf32_ta(acc, ah + kStepK, b_hi, idesc, true);
+            }
           }
-          umma_commit(a_empty + s);
-          umma_commit(x_empty + xb);
+          umma_commit(mma_done + s);
+          }
+          __syncwarp();
         } while (cur.next_step());
-        if (ok) umma_commit(acc_full);
+        if (ok && elect_one()) umma_commit(acc_full);
+        __syncwarp();
       }
-      if (!ok) atomicOr(&g_tc_fault, 2u);
+      if (!ok && lane == 0) atomicOr(&g_tc_fault, 2u);
     }
   } else if (warp >= kWX0) {  // the two warps between the TMA warps and the MMA warps
     // ------------------------------------------------------------ x warps
@@ -234,14 +309,21 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
     bool ok = true;
     UmmaCursor ahead = cur;  // issues the loads, kXBufs steps in front of `cur`
     bool ahead_live = ahead.begin_strip();
-    auto issue = [&]() {  // raw buffer ahead.q % kXBufs is free: its last readers passed the x-warp barrier
+    RingPos xi, xs;          // of the load being issued, of the step being transformed
+    int xkk = ahead_live ? rot_seed % ahead.steps : 0;
+    auto issue = [&]() {  // raw buffer xi.slot is free: its last readers passed the x-warp barrier
       if (!ahead_live) return;
       if (t == 0) {
-        const int xb = ahead.q % kXBufs;
+        const int xb = xi.slot;
         mbar_expect_tx(x_raw + xb, static_cast<unsigned>(kXRawBytes));  // rows >= M are out of range: zero-filled, still counted
-        tma_box_4d(xraw + xb * kXRawBytes, &xmap, ahead.kc * kStepK, 0, part, 0, x_raw + xb);  // all k ranges in one box
+        tma_box_4d(xraw + xb * kXRawBytes, &xmap, xkk * kStepK, 0, part, 0, x_raw + xb);  // all k ranges in one box
       }
-      if (!ahead.next_step()) ahead_live = ahead.begin_strip();
+      xi.advance(kXBufs);
+      xkk = xkk + 1 == ahead.steps ? 0 : xkk + 1;
+      if (!ahead.next_step()) {
+        ahead_live = ahead.begin_strip();
+        if (ahead_live) xkk = rot_seed % ahead.steps;
+      }
     };
     for (int i = 0; i < kXBufs; ++i) issue();
     // A quarter warp moves an 8-row x 8-k-group block along its diagonals: lane i takes k group i of row
@@ -251,9 +333,10 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
     const int mg = (qw >> 1) & 1, kg = (qw & 1) * 8 + li, r0 = (qw >> 2) * 4;
     while (cur.begin_strip()) {
       do {
-        const int xb = cur.q % kXBufs;
-        if (ok) ok = mbar_wait(x_raw + xb, (cur.q / kXBufs) & 1);
-        if (ok && cur.q >= kXBufs) ok = mbar_wait(x_empty + xb, ((cur.q / kXBufs) - 1) & 1);
+        const int xb = xs.slot;
+        if (ok) ok = mbar_wait(x_raw + xb, xs.parity);
+        if (ok) ok = mbar_wait(mma_done + xb, xs.parity ^ 1u);  // the MMAs that read these images two steps ago
+        xs.advance(kXBufs);
         if (ok) {
           for (int ks = 0; ks < cur.split; ++ks) {
             const unsigned char* src = xraw + xb * kXRawBytes + ks * (kStepK * 4) + kg * 16;
@@ -280,6 +363,7 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
       } while (cur.next_step());
     }
     if (!ok && lane == 0) atomicOr(&g_tc_fault, 4u);
+    if (clustered) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   } else {
     // ------------------------------------------------------------ split warps (+ epilogue)
     const int lq = warp & 3, kh = warp >> 2;  // TMEM lane quarter this warp may touch, k half of a step
@@ -288,22 +372,24 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
     const uint32_t a_lane_base = lane_base + kTmemA + kh * (kStepK / 2);
     int strip_i = 0;
     bool ok = true;
+    RingPos w, st;
     while (cur.begin_strip()) {
       const int qpk = 4 / cur.split;
       const int ks = lq / qpk, uq = lq % qpk;   // this quarter's k range and unit of the strip
       const bool warp_live = uq < cur.units;    // warp-uniform: a quarter without columns writes nothing
       const int col = (cur.unit + uq) * 32 + lane;
       const int split = cur.split;
-      const int naccs = min(acc_cols / (16 * S), cur.steps);
+      const int naccs = min(min(acc_cols / (acc_w * S), cur.steps), a.max_accs);
       const int pitch = cur.units * 32;  // KN: floats per k row of the tile
       do {
-        const int buf = cur.q % kRing, s = cur.q % kStages;
-        if (ok) ok = mbar_wait(w_full + buf, (cur.q / kRing) & 1);
-        if (ok && cur.q >= kStages) ok = mbar_wait(a_empty + s, ((cur.q / kStages) - 1) & 1);
+        const int buf = w.slot, s = st.slot;
+        if (ok) ok = mbar_wait(w_full + buf, w.parity);
+        if (ok) ok = mbar_wait(mma_done + s, st.parity ^ 1u);
+        w.advance(kRing), st.advance(kStages);
         if (ok && warp_live) {
           tc_fence_after();
           // NK: this quarter's own tile; KN: the tile of its k range, [64 k][32 u columns], this quarter's columns at 32 uq
-          const unsigned char* tile = ring + buf * kStepBytes + (NK ? lq : lq - uq) * kQuarterBytes;
+          const unsigned char* tile = ring + buf * slot_bytes + (NK ? lq : lq - uq) * kQuarterBytes;
 #pragma unroll
           for (int g = 0; g < kStepK / 2 / 16; ++g) {  // 16 k at a time
             uint32_t hi[16], lo[16];
@@ -338,24 +424,35 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
       } while (cur.next_step());
       // ---- epilogue of the strip: warps 0-3 read their own lane quarter of the accumulators
       float sum[16];
+      float bias_v = 0.0f;
+      const bool stores = warp < 4 && warp_live && ks == 0 && part == 0 && col < a.n;  // this thread writes a column of y
+      if (stores && a.bias) bias_v = __ldg(a.bias + col);  // in flight while the last MMAs complete
       if (warp < 4) {
         if (ok) ok = mbar_wait(acc_full, strip_i & 1);
         if (ok && warp_live) {
           tc_fence_after();
+          // one accumulator per round: its loads (hi.hi + lo.hi columns, and hi.lo columns in the wide form) go out
+          // together and are waited for once; fixed order of additions
           for (int i = 0; i < issuers; ++i) {
             for (int sel = 0; sel < naccs; ++sel) {
-              uint32_t r[16];
-              tmem_ld16(lane_base + i * acc_cols + sel * 16 * S + ks * 16, r);  // the 16 columns of this quarter's own k range
+              uint32_t r0[16], r1[16];
+              const uint32_t t0 = lane_base + i * acc_cols + sel * acc_w * S + ks * 16;
+              tmem_ld16_issue(t0, r0);
+              if (a.wide) tmem_ld16_issue(t0 + 16 * S, r1);
+              tmem_ld_wait16(r0);
+              if (a.wide) tmem_ld_wait16(r1);
 #pragma unroll
-              for (int m = 0; m < 16; ++m)
-                sum[m] = (i == 0 && sel == 0) ? __uint_as_float(r[m]) : __fadd_rn(sum[m], __uint_as_float(r[m]));
+              for (int m = 0; m < 16; ++m) {
+                float v = __uint_as_float(r0[m]);
+                if (a.wide) v = __fadd_rn(v, __uint_as_float(r1[m]));
+                sum[m] = (i == 0 && sel == 0) ? v : __fadd_rn(sum[m], v);
+              }
             }
           }
           tc_fence_before();
           if (split > 1) {
 #pragma unroll
-            for (int m = 0; m < 16; m += 4)
-              *reinterpret_cast<float4*>(red + c * 16 + m) = make_float4(sum[m], sum[m + 1], sum[m + 2], sum[m + 3]);
+            for (int m = 0; m < 16; m += 4) red[(m >> 2) * 128 + c] = make_float4(sum[m], sum[m + 1], sum[m + 2], sum[m + 3]);
           }
         }
       }
@@ -364,7 +461,11 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
         if (warp < 4 && ok && warp_live && ks == 0) {
           for (int j = 1; j < split; ++j)  // fixed order: k range 0 + 1 + 2 + 3
 #pragma unroll
-            for (int m = 0; m < 16; ++m) sum[m] = __fadd_rn(sum[m], red[(c + j * qpk * 32) * 16 + m]);
+            for (int m = 0; m < 16; m += 4) {
+              const float4 v = red[(m >> 2) * 128 + c + j * qpk * 32];
+              sum[m] = __fadd_rn(sum[m], v.x), sum[m + 1] = __fadd_rn(sum[m + 1], v.y);
+              sum[m + 2] = __fadd_rn(sum[m + 2], v.z), sum[m + 3] = __fadd_rn(sum[m + 3], v.w);
+            }
         }
       }
       const bool owner = warp < 4 && ok && warp_live && ks == 0;  // this thread holds a column's sum over this CTA's K
@@ -373,17 +474,22 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
           // hand the partial sums to the rank-0 CTA: its inbox must be free (it has read the previous strip's)
           if (ok && strip_i > 0) ok = mbar_wait_cluster(inbox_free, (strip_i - 1) & 1);
           if (owner) {
-            const uint32_t dst = cluster_map(inbox + (static_cast<size_t>(part - 1) * 128 + c) * 16, 0u);
+            const uint32_t dst = cluster_map(inbox + (part - 1) * 512 + c, 0u);
 #pragma unroll
-            for (int m = 0; m < 16; m += 4) cluster_store_f4(dst + m * 4, make_float4(sum[m], sum[m + 1], sum[m + 2], sum[m + 3]));
+            for (int m = 0; m < 16; m += 4)
+              cluster_store_f4(dst + (m >> 2) * 128 * 16, make_float4(sum[m], sum[m + 1], sum[m + 2], sum[m + 3]));
           }
           cluster_arrive(cluster_map(inbox_full, 0u));  // all 128 epilogue threads arrive, with or without data
         } else {
           if (ok) ok = mbar_wait_cluster(inbox_full, strip_i & 1);
           if (owner && ok) {
-            for (int p = 1; p < a.kparts; ++p)  // fixed order: part 0 + 1 + 2 + 3
+            for (int p = 1; p < a.kparts; ++p)  // fixed order: part 0 + 1 + 2 + ...
 #pragma unroll
-              for (int m = 0; m < 16; ++m) sum[m] = __fadd_rn(sum[m], inbox[(static_cast<size_t>(p - 1) * 128 + c) * 16 + m]);
+              for (int m = 0; m < 16; m += 4) {
+                const float4 v = inbox[(p - 1) * 512 + (m >> 2) * 128 + c];
+                sum[m] = __fadd_rn(sum[m], v.x), sum[m + 1] = __fadd_rn(sum[m + 1], v.y);
+                sum[m + 2] = __fadd_rn(sum[m + 2], v.z), sum[m + 3] = __fadd_rn(sum[m + 3], v.w);
+              }
           }
           asm volatile("bar.sync 3, 128;" ::: "memory");  // warps 0-3: every inbox slot has been read
           // Tell the other parts only when another strip follows: after their last hand-over they may have exited,
@@ -392,11 +498,10 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
             for (int p = 1; p < a.kparts; ++p) cluster_arrive(cluster_map(inbox_free, static_cast<unsigned>(p)));
         }
       }
-      if (owner && ok && part == 0 && col < a.n) {
-        const float bv = a.bias ? a.bias[col] : 0.0f;
+      if (stores && ok) {
 #pragma unroll
         for (int m = 0; m < 16; ++m)
-          if (m < a.m) peer_store(a.out, m, col, __fadd_rn(sum[m], bv));
+          if (m < a.m) peer_store(a.out, m, col, __fadd_rn(sum[m], bias_v));
       }
       // all 256 threads meet before the next strip's stages can reach the MMA warps (a_full needs all of them),
       // so the next strip's first MMAs cannot overwrite TMEM (nor its partials the shared buffer) while they are read
@@ -408,26 +513,80 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
 
   tc_fence_before();
   __syncthreads();
-  if (warp == kWTma) {
+  if (warp == kWMma0) {
     tc_fence_after();
     tmem_dealloc<kTmemCols>(tmem_base);
   }
 }
 
-// Grid, K split, ring depth and dynamic shared memory of a launch (fills a.total_units, a.ctas, a.split, a.ring).
+// How many clusters of `parts` one-CTA-per-SM blocks the device runs at once.  A cluster must sit inside one GPC, so
+// this is less than SMs / parts; the driver is asked once per cluster size, and without a device (plan
+// introspection on a build host) the answer defaults to what a 148-SM B200 gives.
+int resident_clusters(int parts) {
+  static int cached[kMaxParts + 1] = {};
+  if (parts == 1) return sm_count();
+  if (cached[parts] > 0) return cached[parts];
+  const int sms = sm_count();
+  int fit = parts == 2 ? sms / 2 : (parts == 4 ? (sms >= 132 ? 33 : sms / 6) : (sms >= 132 ? 16 : sms / 12));
+  int devices = 0;
+  if (cudaGetDeviceCount(&devices) == cudaSuccess && devices > 0) {
+    auto kernel = gemv_tc_kernel<false>;
+    const int smem = 220 * 1024;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1, attr.val.clusterDim.y = static_cast<unsigned>(parts), attr.val.clusterDim.z = 1;
+    cfg.gridDim = dim3(sms / parts, parts), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem, cfg.attrs = &attr, cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+        cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0)
+      fit = n < sms / parts ? n : sms / parts;
+  }
+  (void)cudaGetLastError();
+  if (fit < 1) fit = 1;
+  return cached[parts] = fit;
+}
+
+// Grid, K splits, ring depth and dynamic shared memory of a launch (fills a.total_units, a.ctas, a.split, a.kparts,
+// a.ring).  K can be split two ways: over the TMEM lane quarters of a CTA (S: cheap to add up, but a 64-k step then
+// carries S x 16 operand rows and takes ~0.62 / 0.85 / 1.3 us of MMA issue for S = 1 / 2 / 4) and over the CTAs of a
+// cluster (parts: full-rate steps, one hand-over per strip through distributed shared memory).  The plan minimises
+// the modelled time: the busiest CTA's steps x step time, or the time HBM needs for W if that is longer, plus the
+// hand-overs.
 size_t plan_tc(TcArgs& a, int k, int n) {
   a.total_units = (n + 31) / 32;
-  a.ctas = a.total_units < sm_count() ? a.total_units : sm_count();
-  const int per_cta = (a.total_units + a.ctas - 1) / a.ctas;
-  // Fewer units than half (a quarter) of the SMs: two (four) CTAs of a cluster share every unit along K, so that a
-  // narrow projection -- a column shard of a multi-GPU run -- still uses most of the machine.  Clusters of four
-  // one-CTA-per-SM blocks fit only 33 at a time on this part, hence the tighter bound for four.
-  a.kparts = 1;
-  if (a.total_units * 4 <= 132 && sm_count() >= 132) a.kparts = 4;
-  else if (a.total_units * 2 <= sm_count()) a.kparts = 2;
-  while (a.kparts > 1 && (k % (a.kparts * kStepK) != 0 || k / a.kparts < 4 * kStepK)) a.kparts /= 2;
-  a.split = per_cta == 1 ? 4 : (per_cta == 2 ? 2 : 1);
-  while (a.split > 1 && (k / a.kparts) % (a.split * kStepK) != 0) a.split /= 2;
+  const float step_us[5] = {0.0f, 0.62f, 0.85f, 0.0f, 1.3f};
+  const float hbm_us = static_cast<float>(k) * static_cast<float>(n) * 4.0f / 6.0e6f;
+  static const bool three = getenv("XDK_TC_MMA3") && getenv("XDK_TC_MMA3")[0] == '1';
+  a.wide = three ? 0 : 1;
+  const int acc_w = a.wide ? 32 : 16;
+  const int max_split = kTmemA / kMaxIssuers / acc_w;  // an accumulator must fit an issuer's columns
+  float best = 1e30f;
+  a.kparts = 0, a.split = 1, a.ctas = 0;
+  for (int parts = 1; parts <= kMaxParts; parts *= 2) {
+    if (k % (parts * kStepK) != 0 || (parts > 1 && k / parts < 4 * kStepK)) continue;
+    if (k / parts > kMaxKPerCta) continue;  // accuracy: see kMaxKPerCta
+    for (int split = 1; split <= max_split; split *= 2) {
+      if ((k / parts) % (split * kStepK) != 0) continue;
+      const size_t other = kXBufs * static_cast<size_t>(split) * (2 * kXHalf1 + kXRaw1) + kRedBytes * parts + 64 * sizeof(uint64_t);
+      if (other + 3 * kStepBytes > 220 * 1024) continue;  // the W ring needs three steps in flight
+      const int upc = 4 / split;  // units a strip holds
+      int ctas = resident_clusters(parts);
+      if (ctas > a.total_units) ctas = a.total_units;
+      const int units = (a.total_units + ctas - 1) / ctas;  // of the busiest CTA
+      const int strips = (units + upc - 1) / upc;
+      float cost = strips * (k / parts / split / kStepK) * step_us[split];
+      if (cost < hbm_us) cost = hbm_us;
+      if (parts > 1) cost += 0.7f + 0.3f * strips + 0.05f * parts;
+      if (cost < best - 1e-3f) best = cost, a.kparts = parts, a.split = split, a.ctas = ctas;
+    }
+  }
+  if (a.kparts == 0) return 0;  // no admissible split of this K
+  static const int forced_accs = getenv("XDK_TC_NACCS") ? atoi(getenv("XDK_TC_NACCS")) : 0;
+  a.max_accs = forced_accs > 0 ? forced_accs : 64;
+  static const bool no_rotate = getenv("XDK_TC_ROT") && getenv("XDK_TC_ROT")[0] == '0';
+  static const bool no_tight = getenv("XDK_TC_SLOT") && getenv("XDK_TC_SLOT")[0] == '0';
+  a.rotate = no_rotate ? 0 : 1, a.tight_ring = no_tight ? 0 : 1;
   const size_t fixed = kXBufs * static_cast<size_t>(a.split) * (2 * kXHalf1 + kXRaw1) + kRedBytes * a.kparts + 64 * sizeof(uint64_t);
   a.ring = static_cast<int>((220 * 1024 - fixed) / kStepBytes);
   if (a.ring > kMaxRing) a.ring = kMaxRing;
@@ -439,6 +598,7 @@ int launch_tc(const float* x, const float* w, const float* bias, const PeerOut& 
   TcArgs a;
   a.bias = bias, a.out = y, a.m = m, a.k = k, a.n = n;
   const size_t smem = plan_tc(a, k, n);
+  if (smem == 0) return XDK_ERR_LIMIT;
   CUtensorMap wmaps[4], xmap;
   CUtensorMap& wmap = wmaps[0];
   if (NK) {
@@ -475,24 +635,25 @@ int launch_tc(const float* x, const float* w, const float* bias, const PeerOut& 
 bool gemv_tc_eligible(const float* x, const float* w, int64_t m, int64_t k, int64_t n, bool nk) {
   // XDK_GEMV_TC=0 keeps every projection on the CUDA-core kernels (comparison runs)
   static const bool enabled = !(getenv("XDK_GEMV_TC") && getenv("XDK_GEMV_TC")[0] == '0');
-  // K <= 16384: the truncating tensor-core accumulation grows with the number of products an accumulator sums
-  // (K / 16 each); measured against an FP64 product the relative L2 error is 2.4e-6 at K = 4096 and stays inside
-  // the 1e-5 gate up to K = 16384, but reaches 1.5e-5 at K = 32768 -- longer rows stay on the FP32-FMA kernels.
-  return enabled && m > 4 && m <= 16 && k % kStepK == 0 && (nk || n % 4 == 0) && aligned16(x) && aligned16(w) &&
-         k <= kMaxK && n < (1 << 30) && k * n >= (4LL << 20);
+  // the shape must also have a launch plan: a K split that keeps every CTA's share of K inside kMaxKPerCta
+  if (!(enabled && m > 4 && m <= 16 && k % kStepK == 0 && (nk || n % 4 == 0) && aligned16(x) && aligned16(w) && k <= kMaxK &&
+        n < (1 << 30) && k * n >= (4LL << 20)))
+    return false;
+  TcArgs a;
+  return plan_tc(a, static_cast<int>(k), static_cast<int>(n)) != 0;
 }
 
 int launch_gemv_tc(const float* x, const float* w, const float* bias, const PeerOut& y, int m, int k, int n, bool nk, cudaStream_t stream) {
   return nk ? launch_tc<true>(x, w, bias, y, m, k, n, stream) : launch_tc<false>(x, w, bias, y, m, k, n, stream);
 }
 
-bool gemv_tc_plan(int64_t m, int64_t k, int64_t n, bool nk, int32_t out[5]) {
+int gemv_tc_plan(int64_t m, int64_t k, int64_t n, bool nk, int32_t out[5]) {
   alignas(16) static const float aligned_dummy[4] = {0, 0, 0, 0};
-  if (!gemv_tc_eligible(aligned_dummy, aligned_dummy, m, k, n, nk)) return false;
+  if (!gemv_tc_eligible(aligned_dummy, aligned_dummy, m, k, n, nk)) return 0;
   TcArgs a;
   const size_t smem = plan_tc(a, static_cast<int>(k), static_cast<int>(n));
   out[0] = a.ctas * a.kparts, out[1] = a.split, out[2] = a.ring, out[3] = static_cast<int32_t>(smem), out[4] = a.total_units;
-  return true;
+  return a.kparts;
 }
 
 unsigned gemv_tc_fault_word() {

@@ -33,6 +33,18 @@ __device__ __forceinline__ void umma_tf32_ta(uint32_t d_tmem, uint32_t a_tmem, u
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
       : "memory");
 }
+// True in exactly one lane of a converged warp.  A role whose loop the whole warp runs (waits included) and that
+// issues its tcgen05.mma / TMA instructions under this predicate keeps its operands warp-uniform; the same loop
+// run by `if (lane == 0)` alone issued each tcgen05.mma ~120 ns after the previous one.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t is_elected;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(is_elected));
+  return is_elected != 0;
+}
 // 32 lanes (the warp's TMEM lane quarter) x 16 consecutive 32-bit columns
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(

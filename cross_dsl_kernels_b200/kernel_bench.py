@@ -27,7 +27,7 @@ import torch
 
 from . import _native
 from . import workloads as wl
-from .ops import decode_linear, fused_residual_rmsnorm, rope_gqa_paged_kv_append
+from .ops import decode_linear, fused_residual_rmsnorm, paged_decode_attention, rope_gqa_paged_kv_append, swiglu
 from .timing import graph_median_us, rotation_for
 from .w4a16 import w4a16_linear
 
@@ -139,6 +139,44 @@ def bench_w4a16(m: int, k: int, n: int, group: int = 128, peak=None, replays=20,
     return _row(f"w4a16_m{m}_k{k}_n{n}_g{group}" + ("_pdl" if dependent else ""), nbytes, t, sets, peak)
 
 
+def bench_attention(context: int, tokens: int = 16, q_heads: int = 32, kv_heads: int = 8, head_dim: int = 128, page_size: int = 16,
+                    dtype=torch.float16, peak=None, replays=20, check=None, dependent=False) -> dict:
+    """Decode attention of ``tokens`` sequences, each ``context`` positions long, over one shared paged cache.  The
+    rotating sets are disjoint page ranges of that cache (one page table per set), so every call reads K and V
+    that the L2 has not seen for a whole rotation.  ``check(stage, (out, q, k_cache, v_cache, positions, table, ids))``
+    sees call 0."""
+    pages_per_seq = -(-context // page_size)
+    nbytes = 2 * tokens * context * kv_heads * head_dim * dtype.itemsize + 2 * tokens * q_heads * head_dim * dtype.itemsize
+    sets = rotation_for(nbytes, cap=48)
+    g = torch.Generator(device="cuda").manual_seed(context)
+    pages = sets * tokens * pages_per_seq
+    kc = torch.randn(pages, page_size, kv_heads, head_dim, generator=g, device="cuda", dtype=dtype)
+    vc = torch.randn(pages, page_size, kv_heads, head_dim, generator=g, device="cuda", dtype=dtype)
+    q = torch.randn(tokens, q_heads, head_dim, generator=g, device="cuda", dtype=dtype)
+    order = torch.randperm(pages, generator=torch.Generator().manual_seed(context)).reshape(sets, tokens, pages_per_seq).cuda()
+    tables = [order[i].contiguous() for i in range(sets)]
+    positions = torch.full((tokens,), context - 1, dtype=torch.int64, device="cuda")
+    ids = torch.arange(tokens, dtype=torch.int64, device="cuda")
+    ncalls = _calls_per_graph(sets)
+    calls = [(lambda i=i: (paged_decode_attention(q, kc, vc, positions, tables[i % sets], ids, page_size=page_size,
+                                                  dependent_launch=dependent), q, kc, vc, positions, tables[i % sets], ids))
+             for i in range(ncalls)]
+    t = graph_median_us(calls, replays, check=check, mutate=lambda: q.neg_(), poison=lambda outs: [o[0].fill_(float("nan")) for o in outs])
+    name = f"paged_decode_attention_{str(dtype).split('.')[-1]}_t{tokens}_hq{q_heads}_hkv{kv_heads}_d{head_dim}_ctx{context}"
+    return _row(name + ("_pdl" if dependent else ""), nbytes, t, sets, peak)
+
+
+def bench_swiglu(rows: int, width: int, dtype=torch.float16, peak=None, replays=20, check=None, dependent=False) -> dict:
+    nbytes = 3 * rows * width * dtype.itemsize
+    sets = rotation_for(nbytes, cap=48)
+    g = torch.Generator(device="cuda").manual_seed(width)
+    ins = [torch.randn(rows, 2 * width, generator=g, device="cuda", dtype=dtype) for _ in range(sets)]
+    ncalls = _calls_per_graph(sets)
+    calls = [(lambda i=i: (swiglu(ins[i % sets], dependent_launch=dependent), ins[i % sets])) for i in range(ncalls)]
+    t = graph_median_us(calls, replays, check=check, mutate=lambda: ins[0].neg_(), poison=lambda outs: [o[0].fill_(float("nan")) for o in outs])
+    return _row(f"swiglu_{str(dtype).split('.')[-1]}_{rows}x{width}" + ("_pdl" if dependent else ""), nbytes, t, sets, peak)
+
+
 def bench_chain(rank: int = 0, world: int = 1, layers: int = 4, peak=None, replays=20, group=None, exchange: str = "peer",
                 dependent: bool = False, check=None, attention: bool = False) -> dict:
     """Decode-layer chain: ``layers`` layers with distinct weights (more than L2 in total) in one
@@ -215,7 +253,8 @@ def table(which=("rmsnorm", "gemv", "rope", "w4a16"), peak=None, split_sweep=Tru
 
 def one(argv: list[str]) -> dict:
     """``--one rmsnorm ROWS HIDDEN f32|bf16|f16`` | ``--one gemv M K N KN|NK SPLIT [strict]`` |
-    ``--one rope f32|bf16 NHD|HND ROPE_DIM`` | ``--one w4a16 M K N GROUP``; few replays (for profilers)."""
+    ``--one rope f32|bf16 NHD|HND ROPE_DIM`` | ``--one w4a16 M K N GROUP`` | ``--one attention CONTEXT [TOKENS]`` |
+    ``--one swiglu ROWS WIDTH``; few replays (for profilers)."""
     dtypes = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
     op, rest = argv[0], argv[1:]
     if op == "rmsnorm":
@@ -227,6 +266,10 @@ def one(argv: list[str]) -> dict:
         return bench_rope(dtypes[rest[0]], rest[1], int(rest[2]), replays=3)
     if op == "w4a16":
         return bench_w4a16(int(rest[0]), int(rest[1]), int(rest[2]), int(rest[3]), replays=3)
+    if op == "attention":
+        return bench_attention(int(rest[0]), tokens=int(rest[1]) if len(rest) > 1 else 16, replays=3)
+    if op == "swiglu":
+        return bench_swiglu(int(rest[0]), int(rest[1]), replays=3)
     raise SystemExit(one.__doc__)
 
 

@@ -163,10 +163,10 @@ XDK_API int xdk_gemv_f32_v2(const float* x, const float* w, const float* bias, f
                     void* scratch, size_t scratch_bytes, unsigned flags, void* stream);
 /*
  * Introspection (no counterpart in the reference): would xdk_gemv_f32(split_k = 0, scratch = NULL) with 16-byte
- * aligned x and w run this shape on the tensor-core kernel, and with what launch?  Returns 1 and fills
- * out5 = {CTAs, K split over the TMEM lane quarters (1, 2 or 4), W ring depth, dynamic shared memory in bytes,
- * 32-column units}, or 0 when the shape takes another kernel (out5 untouched), or XDK_ERR_ARG for a NULL out5.
- * Launches nothing.
+ * aligned x and w run this shape on the tensor-core kernel, and with what launch?  Returns the cluster size
+ * (1, 2, 4 or 8 CTAs that share each strip of columns along K) and fills out5 = {CTAs in all, K split over the
+ * TMEM lane quarters (1, 2 or 4), W ring depth, dynamic shared memory in bytes, 32-column units}, or 0 when the
+ * shape takes another kernel (out5 untouched), or XDK_ERR_ARG for a NULL out5.  Launches nothing.
  */
 XDK_API int xdk_gemv_tc_plan(int64_t m, int64_t k, int64_t n, int weight_is_nk, int32_t* out5);
 /* Bytes of scratch xdk_gemv_f32 wants for this shape on the current device (0: none needed). */

@@ -51,7 +51,7 @@ def test_header_is_plain_c_and_a_c_program_links(tmp_path):
         "int main(void) {\n"
         "  int32_t plan[5];\n"
         "  if (xdk_abi_version() != 2) return 1;\n"
-        "  if (xdk_gemv_tc_plan(16, 4096, 14336, 0, plan) != 1) return 2;\n"
+        "  if (xdk_gemv_tc_plan(16, 4096, 14336, 0, plan) != 1) return 2;  /* one CTA per strip at this width */\n"
         '  printf("%s %d %d\\n", xdk_strerror(XDK_OK), (int)plan[0], (int)plan[1]);\n'
         "  return 0;\n}\n")
     exe = tmp_path / "probe"
