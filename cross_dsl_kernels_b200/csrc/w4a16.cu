@@ -640,7 +640,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
 
   if (warp == kWTma) {
     // ------------------------------------------------------------ TMA producer: packed codes and scales
-    if (lane == 0) {
+    {  // the whole warp runs the loop (waits included), one elected lane issues: operands stay warp-uniform
       bool ok = true;
       int strip_i = 0;
       while (ok && cur.begin_strip()) {
@@ -649,31 +649,37 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
         // have released the last packed step of the previous strip
         if (strip_i > 0) {
           const int prev = cur.q - 1;
-          ok = mbar_wait(pk_empty + prev % kUPackedBufs, (prev / kUPackedBufs) & 1);
+          ok = __all_sync(0xffffffffu, mbar_wait(pk_empty + prev % kUPackedBufs, (prev / kUPackedBufs) & 1));
           if (!ok) break;
         }
-        mbar_expect_tx(sc_full, static_cast<unsigned>(cur.units * cur.split * 32 * scale_row_bytes));
-        for (int lq = 0; lq < 4; ++lq)
-          if (lq % qpk < cur.units) tma_box_2d(scbuf + lq * 32 * scale_row_bytes, &smap, 0, (cur.unit + lq % qpk) * 32, sc_full);
+        if (elect_one()) {
+          mbar_expect_tx(sc_full, static_cast<unsigned>(cur.units * cur.split * 32 * scale_row_bytes));
+          for (int lq = 0; lq < 4; ++lq)
+            if (lq % qpk < cur.units) tma_box_2d(scbuf + lq * 32 * scale_row_bytes, &smap, 0, (cur.unit + lq % qpk) * 32, sc_full);
+        }
+        __syncwarp();
         do {
           const int buf = cur.q % kUPackedBufs;
-          if (cur.q >= kUPackedBufs && !mbar_wait(pk_empty + buf, ((cur.q / kUPackedBufs) - 1) & 1)) {
-            ok = false;
-            break;
+          if (cur.q >= kUPackedBufs) {
+            ok = __all_sync(0xffffffffu, mbar_wait(pk_empty + buf, ((cur.q / kUPackedBufs) - 1) & 1));
+            if (!ok) break;
           }
-          mbar_expect_tx(pk_full + buf, static_cast<unsigned>(cur.units * cur.split * 32 * (kUStepK / 2)));
-          for (int lq = 0; lq < 4; ++lq)  // 32-row boxes; the 128-byte swizzle depends on (row & 7) only
-            if (lq % qpk < cur.units)
-              tma_box_2d(packed + buf * kUPackedBytes + lq * 32 * (kUStepK / 2), &wmap,
-                         ((lq / qpk) * cur.kper + cur.kc * kUStepK) / 8, (cur.unit + lq % qpk) * 32, pk_full + buf);
+          if (elect_one()) {
+            mbar_expect_tx(pk_full + buf, static_cast<unsigned>(cur.units * cur.split * 32 * (kUStepK / 2)));
+            for (int lq = 0; lq < 4; ++lq)  // 32-row boxes; the 128-byte swizzle depends on (row & 7) only
+              if (lq % qpk < cur.units)
+                tma_box_2d(packed + buf * kUPackedBytes + lq * 32 * (kUStepK / 2), &wmap,
+                           ((lq / qpk) * cur.kper + cur.kc * kUStepK) / 8, (cur.unit + lq % qpk) * 32, pk_full + buf);
+          }
+          __syncwarp();
         } while (cur.next_step());
         ++strip_i;
       }
-      if (!ok) atomicOr(&g_w4_fault, 4u);
+      if (!ok && lane == 0) atomicOr(&g_w4_fault, 4u);
     }
   } else if (warp == kWMma0 || warp >= kWMma1) {
     // ------------------------------------------------------------ MMA issuers
-    if (lane == 0) {
+    {  // whole warp, one elected lane issues (a lane-0-only loop issued a tcgen05.mma only every ~120 ns)
       const int issuer = warp == kWMma0 ? 0 : warp - kWMma1 + 1;
       const uint32_t acc = tmem_base + issuer * kUAccCols;
       // x descriptor: only the 14-bit start-address field changes from MMA to MMA
@@ -685,23 +691,27 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
         const uint32_t idesc = umma_idesc(16 * cur.split, 0u);
         do {
           const int xb = cur.q % kUXBufs, s = cur.q % kUStages;
-          ok = mbar_wait(x_full + xb, (cur.q / kUXBufs) & 1) && mbar_wait(a_full + s, (cur.q / kUStages) & 1);
+          ok = __all_sync(0xffffffffu, mbar_wait(x_full + xb, (cur.q / kUXBufs) & 1) && mbar_wait(a_full + s, (cur.q / kUStages) & 1));
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_base = tmem_base + kUTmemA + s * kUStageCols + issuer * 8;
           const uint32_t x_lo = xd_lo + ((xb * kUXBytes + issuer * 2 * kUXLbo) >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int j = 0; j < kUStepK / 16 / kUIssuers; ++j) {  // K blocks issuer, issuer + 4, ...
-            uint64_t xd;
-            asm("mov.b64 %0, {%1, %2};" : "=l"(xd) : "r"(x_lo + ((j * kUIssuers * 2 * kUXLbo) >> 4)), "r"(xd_hi));
-            umma_f16_ta(acc, a_base + j * kUIssuers * 8, xd, idesc, !(cur.kc == 0 && j == 0));
+            for (int j = 0; j < kUStepK / 16 / kUIssuers; ++j) {  // K blocks issuer, issuer + 4, ...
+              uint64_t xd;
+              asm("mov.b64 %0, {%1, %2};" : "=l"(xd) : "r"(x_lo + ((j * kUIssuers * 2 * kUXLbo) >> 4)), "r"(xd_hi));
+              umma_f16_ta(acc, a_base + j * kUIssuers * 8, xd, idesc, !(cur.kc == 0 && j == 0));
+            }
+            umma_commit(a_empty + s);   // the TMEM stage is free once every issuer's MMAs have read it
+            umma_commit(x_empty + xb);
           }
-          umma_commit(a_empty + s);   // the TMEM stage is free once every issuer's MMAs have read it
-          umma_commit(x_empty + xb);
+          __syncwarp();
         } while (cur.next_step());
-        if (ok) umma_commit(acc_full);
+        if (ok && elect_one()) umma_commit(acc_full);
+        __syncwarp();
       }
-      if (!ok) atomicOr(&g_w4_fault, 8u);
+      if (!ok && lane == 0) atomicOr(&g_w4_fault, 8u);
     }
   } else if (warp >= kWX0) {
     // ------------------------------------------------------------ x warps
@@ -784,21 +794,25 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
           const unsigned char* row = packed + buf * kUPackedBytes + c * (kUStepK / 2);
           const int k_half = k_range0 + cur.kc * kUStepK + kh * (kUStepK / 2);
 #pragma unroll
-          for (int pc = 0; pc < kUStepK / 64; ++pc) {
+          for (int pp = 0; pp < kUStepK / 128; ++pp) {  // two pieces = 64 k = 32 TMEM columns per store
+            // (a tcgen05.st costs the warp ~125 ns whatever its width, so 32 columns go out at once)
+            uint32_t r[32];
             // two pieces = 64 k lie inside one group (group >= 64)
-            const __half2 s2 = __half2half2(sc_row[(k_half + (pc & ~1) * 32) >> scale_shift]);
-            const int piece = kh * (kUStepK / 64) + pc;
-            const U4 wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));  // rows past N are zero-filled: harmless
-            uint32_t r[16];
+            const __half2 s2 = __half2half2(sc_row[(k_half + pp * 64) >> scale_shift]);
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
-              __half2 h[4];
-              dequant8(word, s2, h);
+            for (int half = 0; half < 2; ++half) {
+              const int piece = kh * (kUStepK / 64) + pp * 2 + half;
+              const U4 wv = *reinterpret_cast<const U4*>(row + ((piece ^ (c & 7)) << 4));  // rows past N are zero-filled: harmless
 #pragma unroll
-              for (int i = 0; i < 4; ++i) r[4 * w + i] = *reinterpret_cast<uint32_t*>(&h[i]);
+              for (int w = 0; w < 4; ++w) {
+                const uint32_t word = w == 0 ? wv.x : (w == 1 ? wv.y : (w == 2 ? wv.z : wv.w));
+                __half2 h[4];
+                dequant8(word, s2, h);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) r[16 * half + 4 * w + i] = *reinterpret_cast<uint32_t*>(&h[i]);
+              }
             }
-            tmem_st16(a_lane_base + s * kUStageCols + pc * 16, r);
+            tmem_st32(a_lane_base + s * kUStageCols + pp * 32, r);
           }
           tmem_wait_st();
           tc_fence_before();
