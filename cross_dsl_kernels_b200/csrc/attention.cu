@@ -60,6 +60,11 @@ __device__ __forceinline__ void merge_stats(float& m_a, float& l_a, float& scale
   m_a = m;
 }
 
+template <typename T, int D>
+struct StageV {  // whether a warp's V rows are staged in shared memory beside its K rows
+  static constexpr bool value = static_cast<size_t>(kAttnWarps) * 32 * (2 * D * sizeof(T) + 16) <= 72 * 1024;
+};
+
 template <typename T, int G, int D>
 __global__ void __launch_bounds__(kAttnThreads)
 paged_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -70,8 +75,13 @@ paged_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_c
   static_assert(D % 32 == 0 && D % E == 0, "head_dim must be a multiple of 32");
   constexpr int kRowPitch = D * static_cast<int>(sizeof(T)) + 16;  // bytes; the pad spreads the lanes' rows over the banks
   extern __shared__ __align__(16) unsigned char attn_smem[];
-  // [warp][32 rows][kRowPitch] K tiles; reused after the loop for the warps' accumulators [warp][G][D] floats
-  unsigned char* ktile = attn_smem + warp_of(threadIdx.x) * 32 * kRowPitch;
+  constexpr int kVPitch = D * static_cast<int>(sizeof(T));         // V rows are read along the row: no pad needed
+  // V is staged beside K while that leaves room for three CTAs per SM; longer rows read V straight from global memory
+  constexpr bool kStageV = StageV<T, D>::value;
+  constexpr int kWarpTile = 32 * (kRowPitch + (kStageV ? kVPitch : 0));
+  // [warp][32 K rows of kRowPitch | 32 V rows]; reused after the loop for the warps' accumulators [warp][G][D] floats
+  unsigned char* ktile = attn_smem + warp_of(threadIdx.x) * kWarpTile;
+  unsigned char* vtile = ktile + 32 * kRowPitch;
   float (*part_acc)[G][D] = reinterpret_cast<float (*)[G][D]>(attn_smem);
   __shared__ __align__(16) float qs[G][D];                 // q of the group, pre-multiplied by scale
   __shared__ __align__(16) float probs[kAttnWarps][32][G];  // the tile's probabilities, [position][head]
@@ -116,11 +126,19 @@ paged_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_c
     }
     rows[warp][lane] = row;  // dead positions point at row 0: a valid address, and their probability is 0
     __syncwarp();
-    // the tile's K rows into shared memory: chunk c = 16-byte piece (c % PIECES) of row (c / PIECES)
+    // the tile's K and V rows into shared memory: chunk c = 16-byte piece (c % PIECES) of row (c / PIECES).  Both
+    // go out together, so a tile costs one trip to HBM (V read row by row after the scores cost eight more)
 #pragma unroll
     for (int i = 0; i < PIECES; ++i) {
       const int c = i * 32 + lane, r = c / PIECES, p = c - r * PIECES;
       cp_async16(ktile + r * kRowPitch + p * 16, reinterpret_cast<const unsigned char*>(k_cache + rows[warp][r]) + p * 16);
+    }
+    if constexpr (kStageV) {
+#pragma unroll
+      for (int i = 0; i < PIECES; ++i) {
+        const int c = i * 32 + lane, r = c / PIECES, p = c - r * PIECES;
+        cp_async16(vtile + r * kVPitch + p * 16, reinterpret_cast<const unsigned char*>(v_cache + rows[warp][r]) + p * 16);
+      }
     }
     cp_async_wait_all();
     __syncwarp();
@@ -171,6 +189,32 @@ paged_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_c
       for (int e = 0; e < DPL; ++e) acc[g][e] *= corr[g];
     const int64_t left = ctx - (tile * kAttnThreads + warp * 32);
     const int n_live = left >= 32 ? 32 : (left > 0 ? static_cast<int>(left) : 0);
+    if constexpr (kStageV) {
+    for (int j0 = 0; j0 < n_live; ++j0) {
+      float vf[DPL];
+      const T* vp = reinterpret_cast<const T*>(vtile + j0 * kVPitch) + lane * DPL;
+      if constexpr (DPL * sizeof(T) == 8) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(vp);
+        const T* ve = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) vf[e] = Elem<T>::to_f32(ve[e]);
+      } else if constexpr (DPL * sizeof(T) == 16) {
+        const U4 raw = *reinterpret_cast<const U4*>(vp);
+        const T* ve = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) vf[e] = Elem<T>::to_f32(ve[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) vf[e] = Elem<T>::to_f32(vp[e]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float p = probs[warp][j0][g];
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(p, vf[e], acc[g][e]);
+      }
+    }
+    } else {
     // four positions per pass, their V loads issued together (dead positions carry probability 0 and row 0)
     for (int j0 = 0; j0 < n_live; j0 += 4) {
       float vf[4][DPL];
@@ -200,6 +244,7 @@ paged_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_c
 #pragma unroll
           for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(p, vf[u][e], acc[g][e]);
         }
+    }
     }
     __syncwarp();  // the tile's shared entries are free for the next tile
   }
@@ -263,7 +308,7 @@ int launch_attention_cluster(const void* q, const void* kc, const void* vc, void
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(splits), static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(tokens));
   cfg.blockDim = dim3(kAttnThreads);
-  constexpr size_t tile_bytes = static_cast<size_t>(kAttnWarps) * 32 * (D * sizeof(T) + 16);
+  constexpr size_t tile_bytes = static_cast<size_t>(kAttnWarps) * 32 * ((StageV<T, D>::value ? 2 : 1) * D * sizeof(T) + 16);
   constexpr size_t acc_bytes = static_cast<size_t>(kAttnWarps) * G * D * sizeof(float);
   constexpr size_t smem = tile_bytes > acc_bytes ? tile_bytes : acc_bytes;
   if (smem > 48 * 1024) {
@@ -339,9 +384,12 @@ extern "C" int xdk_paged_decode_attention(const void* q, const void* k_cache, co
   a.q_heads = static_cast<int>(q_heads), a.kv_heads = static_cast<int>(kv_heads);
   a.hnd = cache_is_hnd ? 1 : 0;
   a.scale = scale;
-  // Context splits: enough CTAs for about four per SM, at most one split per 128-position tile of the longest
+  // Context splits: as many CTAs as the SMs hold at once, at most one split per 128-position tile of the longest
   // context the caller expects (context_hint; <= 0: assume long contexts), at most the portable cluster size.
-  int splits = static_cast<int>((4LL * sm_count() + tokens * kv_heads - 1) / (tokens * kv_heads));
+  const int64_t elem = dtype == XDK_F32 ? 4 : 2;
+  const bool staged = kAttnWarps * 32 * (2 * head_dim * elem + 16) <= 72 * 1024;  // StageV of the kernel that will run
+  const int64_t resident = staged ? 3 : 4;                                          // CTAs an SM holds at once
+  int splits = static_cast<int>(resident * sm_count() / (tokens * kv_heads));      // one wave, never a partial second one
   if (context_hint > 0) {
     const int64_t tiles = (context_hint + kAttnThreads - 1) / kAttnThreads;
     if (splits > tiles) splits = static_cast<int>(tiles);

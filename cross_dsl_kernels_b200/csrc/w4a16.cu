@@ -1001,12 +1001,15 @@ extern "C" int xdk_w4a16_peer(const void* x, const uint8_t* packed, const void* 
   const bool dependent = (flags & XDK_DEPENDENT_LAUNCH) != 0;
   a.out = out;
   const bool vec_ok = k % 32 == 0 && aligned16(packed) && aligned16(x);  // 16-byte vectors of 32 codes
-  // M > 8, and every M whose output is strided or goes to several ranks: the tcgen05 kernel (measured at K = 4096,
-  // M = 16 against the mma.sync kernel: 10.0 vs 12.5 us at N = 4096, 12.8 vs 15.9 at 6144, 17.5 vs 26.0 at 14336,
-  // 31.1 vs 42.4 at 28672).  XDK_W4A16_UMMA=0 sends M > 8 to the mma.sync kernel instead (comparison runs).
+  // M >= 3 (M = 2 on large matrices), and every M whose output is strided or goes to several ranks: the tcgen05
+  // kernel.  Its time hardly depends on M (K = 4096, N = 14336: 17.1 us at M = 1, 17.6 at M = 8, 18.2 at M = 16),
+  // so it beats the mma.sync kernel from M = 3 on (24.9 us at M = 4, 25.3 at M = 8; N = 4096: 10.3 vs 10.7 and
+  // 10.5 vs 11.3) and the SIMT kernel at M = 2 on large matrices (17.2 vs 20.6 us; N = 4096: 10.2 vs 7.4, SIMT
+  // stays).  XDK_W4A16_UMMA=0 keeps it for strided and multi-rank outputs only (comparison runs).
   static const int umma_env = getenv("XDK_W4A16_UMMA") ? (getenv("XDK_W4A16_UMMA")[0] == '1' ? 1 : 0) : -1;
   const bool umma_ok = vec_ok && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales);
-  if (umma_ok && ((umma_env != 0 && m > 8) || !plain)) {
+  const int umma_min_m = k * n >= (32LL << 20) ? 2 : 3;
+  if (umma_ok && ((umma_env != 0 && m >= umma_min_m) || !plain)) {
     const int st = launch_umma(a, dependent, s);
     if (st != XDK_ERR_LIMIT || !plain) return st;
   }
