@@ -94,16 +94,6 @@ struct TcArgs {
   int tight_ring; // 1: a CTA whose strips are narrower than 128 columns cuts the ring into smaller, more slots
 };
 
-// Position in a ring of `depth` buffers guarded by full/empty mbarriers: the slot and the parity a consumer waits
-// for on the slot's "full" barrier; a producer waits for parity ^ 1 on the "empty" barrier (which a fresh barrier
-// already satisfies).  Kept by increments: the roles' loops are latency chains, a division per step shows.
-struct RingPos {
-  int slot = 0;
-  uint32_t parity = 0;
-  __device__ __forceinline__ void advance(int depth) {
-    if (++slot == depth) slot = 0, parity ^= 1u;
-  }
-};
 
 __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {  // no wait: see tmem_ld_wait16
   asm volatile(

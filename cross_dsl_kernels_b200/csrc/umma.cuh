@@ -154,6 +154,17 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, unsigned parity
   }
 }
 
+// Position in a ring of `depth` buffers guarded by full/empty mbarriers: the slot and the parity a consumer waits
+// for on the slot's "full" barrier; a producer waits for parity ^ 1 on the "empty" barrier (which a fresh barrier
+// already satisfies).  Kept by increments: the roles' loops are latency chains, a division per step shows.
+struct RingPos {
+  int slot = 0;
+  uint32_t parity = 0;
+  __device__ __forceinline__ void advance(int depth) {
+    if (++slot == depth) slot = 0, parity ^= 1u;
+  }
+};
+
 // The K split of a strip of `units` 32-column units: a warp may touch only the TMEM lane quarter warp % 4, so a
 // strip narrower than 128 columns spreads S k ranges over the quarters instead (S = 4 for 1 unit, 2 for <= 2).
 __host__ __device__ inline int umma_split(int units, int k, int step_k) {

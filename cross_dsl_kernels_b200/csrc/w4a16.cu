@@ -565,16 +565,14 @@ int launch_stream(const W4Args& a, cudaStream_t stream) {
 // frees its TMEM columns before it returns.
 constexpr int kUStepK = 256;                   // k per step: one packed box row (128 bytes), one A stage
 constexpr int kUPackedBufs = 4;                // packed steps in flight (16 KB each)
-constexpr int kUStages = 2;                    // A operand stages in TMEM
-constexpr int kUXBufs = 2;                     // x step buffers (raw and operand layout each)
+constexpr int kUMaxStages = 3;                 // A operand stages in TMEM: 3 while the accumulators fit 128 columns, else 2
+constexpr int kUMaxXBufs = 4;                  // x step buffers (raw and operand layout each): 4 unless a strip splits K four ways
 constexpr int kUIssuers = 4;                   // MMA-issuing warps, one accumulator each
-constexpr int kUTmemCols = 512;                // allocation (power of two)
-constexpr int kUAccCols = 64;                  // TMEM columns reserved per issuer (16 S <= 64)
-constexpr int kUTmemA = kUIssuers * kUAccCols; // first column of A stage 0
+constexpr int kUTmemCols = 512;                // allocation (power of two): accumulators first, then the stages
 constexpr int kUStageCols = kUStepK / 2;       // 32-bit TMEM columns per stage (two FP16 k per column)
-static_assert(kUTmemA + kUStages * kUStageCols <= kUTmemCols, "A stages must fit the TMEM allocation");
 constexpr int kUXLbo = 128, kUXSbo = (kUStepK / 8) * kUXLbo;  // x: [row group of 8][32 k groups][8 rows x 16 B]
-constexpr int kUXBytes = 8 * kUXSbo;           // up to 64 rows (S = 4)
+constexpr int kUXBytes = 8 * kUXSbo;           // an x buffer for 64 rows (S = 4); the x region is 2 x 2 of these
+constexpr int kUXRegion = 2 * kUXBytes;        // bytes of all operand images (and again of all raw buffers)
 constexpr int kUPackedBytes = 4 * 32 * (kUStepK / 2);  // 4 lane quarters x 32 rows x 128 B
 constexpr int kURedBytes = 128 * 16 * 4;       // k-range partials: [lane][16] floats
 constexpr int kWTma = 8, kWMma0 = 9, kWX0 = 10, kWMma1 = 12;  // warp roles; 0-7 unpack, 10-11 x, 12-14 MMA
@@ -582,6 +580,9 @@ constexpr int kUThreads = 15 * 32;
 
 struct UmmaPlan {
   int ctas, total_units;  // 32-column units
+  int smax;               // widest K split (lane quarters) any strip of the launch uses: sizes the x buffers
+  int xdepth;             // x buffers in flight: the x region cut into buffers of smax x 8 KB, at most kUMaxXBufs
+  int stages;             // A stages in TMEM
 };
 
 __global__ void __launch_bounds__(kUThreads, 1)
@@ -589,20 +590,26 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
                   const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* packed = smem_raw;                                 // [kUPackedBufs][kUPackedBytes]
-  unsigned char* xbuf = packed + kUPackedBufs * kUPackedBytes;      // [kUXBufs][kUXBytes]
-  unsigned char* xraw = xbuf + kUXBufs * kUXBytes;                  // [kUXBufs][4 k ranges][16 rows][256 k] as TMA lands it
-  unsigned char* scbuf = xraw + kUXBufs * kUXBytes;                 // [128 lanes][scale_row_bytes]
+  // A step's x is smax k ranges of [16 rows][256 k] = smax x 8 KB, raw as TMA lands it and again as operand image.
+  // With a small smax the same memory holds more steps: the x path (TMA -> x warps -> MMA -> buffer free) is a loop of
+  // ~1.4 us, which with two buffers set the step time of the whole kernel.
+  const int xstride = plan.smax * 2 * kUXSbo, xdepth = plan.xdepth;
+  const int kUStages = plan.stages;
+  const int kUAccCols = (kUTmemCols - kUStages * kUStageCols) / kUIssuers, kUTmemA = kUIssuers * kUAccCols;
+  unsigned char* xbuf = packed + kUPackedBufs * kUPackedBytes;      // [xdepth][xstride] operand images
+  unsigned char* xraw = xbuf + kUXRegion;                           // [xdepth][smax k ranges][16 rows][256 k] as TMA lands it
+  unsigned char* scbuf = xraw + kUXRegion;                          // [128 lanes][scale_row_bytes]
   const int scale_row_bytes = a.groups * 2;
   float* red = reinterpret_cast<float*>(scbuf + 128 * scale_row_bytes);  // [128 lanes][16]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(red) + kURedBytes);
   uint64_t* pk_full = bars;                       // [kUPackedBufs]  TMA bytes of a packed step landed
   uint64_t* pk_empty = pk_full + kUPackedBufs;    // [kUPackedBufs]  the 8 unpack warps are done with the step
-  uint64_t* a_full = pk_empty + kUPackedBufs;     // [kUStages] the 8 unpack warps wrote the stage to TMEM
-  uint64_t* a_empty = a_full + kUStages;          // [kUStages] every issuer's MMAs that read the stage completed
-  uint64_t* x_raw = a_empty + kUStages;           // [kUXBufs] TMA bytes of an x step landed
-  uint64_t* x_full = x_raw + kUXBufs;             // [kUXBufs] both x warps reordered their share
-  uint64_t* x_empty = x_full + kUXBufs;           // [kUXBufs] every issuer's MMAs that read the buffer completed
-  uint64_t* sc_full = x_empty + kUXBufs;          // [1]
+  uint64_t* a_full = pk_empty + kUPackedBufs;     // [kUMaxStages] the 8 unpack warps wrote the stage to TMEM
+  uint64_t* a_empty = a_full + kUMaxStages;       // [kUMaxStages] every issuer's MMAs that read the stage completed
+  uint64_t* x_raw = a_empty + kUMaxStages;        // [kUMaxXBufs] TMA bytes of an x step landed
+  uint64_t* x_full = x_raw + kUMaxXBufs;          // [kUMaxXBufs] both x warps reordered their share
+  uint64_t* x_empty = x_full + kUMaxXBufs;        // [kUMaxXBufs] every issuer's MMAs that read the buffer completed
+  uint64_t* sc_full = x_empty + kUMaxXBufs;       // [1]
   uint64_t* acc_full = sc_full + 1;               // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
 
@@ -617,7 +624,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       mbar_init(pk_full + i, 1);
       mbar_init(pk_empty + i, 8);   // one arrival per unpack warp
     }
-    for (int i = 0; i < kUXBufs; ++i) {
+    for (int i = 0; i < xdepth; ++i) {
       mbar_init(x_raw + i, 1);
       mbar_init(x_full + i, 1);     // one x thread, after the x warps met
       mbar_init(x_empty + i, kUIssuers);
@@ -686,16 +693,18 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       const uint64_t xd0 = umma_desc(smem_u32(xbuf), kUXLbo, kUXSbo);
       const uint32_t xd_lo = static_cast<uint32_t>(xd0), xd_hi = static_cast<uint32_t>(xd0 >> 32);
       bool ok = true;
+      RingPos xp, sp;
       while (ok && cur.begin_strip()) {
         // D = F32, A = B = F16 K-major, N = 16 S, M = 128
         const uint32_t idesc = umma_idesc(16 * cur.split, 0u);
         do {
-          const int xb = cur.q % kUXBufs, s = cur.q % kUStages;
-          ok = __all_sync(0xffffffffu, mbar_wait(x_full + xb, (cur.q / kUXBufs) & 1) && mbar_wait(a_full + s, (cur.q / kUStages) & 1));
+          const int xb = xp.slot, s = sp.slot;
+          ok = __all_sync(0xffffffffu, mbar_wait(x_full + xb, xp.parity) && mbar_wait(a_full + s, sp.parity));
           if (!ok) break;
+          xp.advance(xdepth), sp.advance(kUStages);
           tc_fence_after();
           const uint32_t a_base = tmem_base + kUTmemA + s * kUStageCols + issuer * 8;
-          const uint32_t x_lo = xd_lo + ((xb * kUXBytes + issuer * 2 * kUXLbo) >> 4);
+          const uint32_t x_lo = xd_lo + ((xb * xstride + issuer * 2 * kUXLbo) >> 4);
           if (elect_one()) {
 #pragma unroll
             for (int j = 0; j < kUStepK / 16 / kUIssuers; ++j) {  // K blocks issuer, issuer + 4, ...
@@ -717,20 +726,22 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
     // ------------------------------------------------------------ x warps
     const int t = threadIdx.x - kWX0 * 32;  // 0 .. 63
     bool ok = true;
-    UmmaCursor ahead = cur;  // issues the loads, kUXBufs steps in front of `cur`
+    UmmaCursor ahead = cur;  // issues the loads, xdepth steps in front of `cur`
     bool ahead_live = ahead.begin_strip();
-    auto issue = [&]() {  // raw buffer ahead.q % kUXBufs is free: its last readers passed the x-warp barrier
+    RingPos xi, xs;          // of the load being issued, of the step being reordered
+    auto issue = [&]() {  // raw buffer xi.slot is free: its last readers passed the x-warp barrier
       if (!ahead_live) return;
       if (t == 0) {
-        const int xb = ahead.q % kUXBufs;
+        const int xb = xi.slot;
         mbar_expect_tx(x_raw + xb, static_cast<unsigned>(ahead.split * 16 * kUStepK * 2));
         for (int ks = 0; ks < ahead.split; ++ks)  // rows >= M are out of range: zero-filled, still counted
-          tma_box_2d(xraw + xb * kUXBytes + ks * 16 * kUStepK * 2, &xmap, ks * ahead.kper + ahead.kc * kUStepK, 0, x_raw + xb);
+          tma_box_2d(xraw + xb * xstride + ks * 16 * kUStepK * 2, &xmap, ks * ahead.kper + ahead.kc * kUStepK, 0, x_raw + xb);
       }
+      xi.advance(xdepth);
       if (!ahead.next_step()) ahead_live = ahead.begin_strip();
     };
     if (t == 0) pdl_wait();  // x is the preceding kernel's output; packed codes and scales (issued already) are not
-    for (int i = 0; i < kUXBufs; ++i) issue();
+    for (int i = 0; i < xdepth; ++i) issue();
     // A quarter warp moves an 8-row x 8-k-group block per pass along its diagonals: lane i takes k group i of row
     // (i + r) & 7, so the eight 16-byte loads (row pitch 512 B) and the eight stores (k-group pitch 128 B) each hit
     // eight different bank groups.
@@ -738,13 +749,14 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
     const int mg = qw >> 2, kg = (qw & 3) * 8 + li;
     while (cur.begin_strip()) {
       do {
-        const int xb = cur.q % kUXBufs;
-        if (ok) ok = mbar_wait(x_raw + xb, (cur.q / kUXBufs) & 1);
-        if (ok && cur.q >= kUXBufs) ok = mbar_wait(x_empty + xb, ((cur.q / kUXBufs) - 1) & 1);
+        const int xb = xs.slot;
+        if (ok) ok = mbar_wait(x_raw + xb, xs.parity);
+        if (ok) ok = mbar_wait(x_empty + xb, xs.parity ^ 1u);  // a fresh barrier passes: nothing has read the buffer yet
+        xs.advance(xdepth);
         if (ok) {
           for (int ks = 0; ks < cur.split; ++ks) {
-            const unsigned char* src = xraw + xb * kUXBytes + ks * 16 * kUStepK * 2 + kg * 16;
-            unsigned char* dst = xbuf + xb * kUXBytes + (ks * 2 + mg) * kUXSbo + kg * kUXLbo;
+            const unsigned char* src = xraw + xb * xstride + ks * 16 * kUStepK * 2 + kg * 16;
+            unsigned char* dst = xbuf + xb * xstride + (ks * 2 + mg) * kUXSbo + kg * kUXLbo;
             U4 v[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r) v[r] = *reinterpret_cast<const U4*>(src + (mg * 8 + ((li + r) & 7)) * (kUStepK * 2));
@@ -775,6 +787,7 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
     const __half* sc_row = reinterpret_cast<const __half*>(scbuf + c * scale_row_bytes);
     int strip_i = 0;
     bool ok = true;
+    RingPos sp;
     while (cur.begin_strip()) {
       const int qpk = 4 / cur.split;
       const int ks = lq / qpk, uq = lq % qpk;   // this quarter's k range and unit of the strip
@@ -784,9 +797,10 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
       const int split = cur.split;
       if (ok) ok = mbar_wait(sc_full, strip_i & 1);
       do {
-        const int buf = cur.q % kUPackedBufs, s = cur.q % kUStages;
+        const int buf = cur.q % kUPackedBufs, s = sp.slot;
         if (ok) ok = mbar_wait(pk_full + buf, (cur.q / kUPackedBufs) & 1);
-        if (ok && cur.q >= kUStages) ok = mbar_wait(a_empty + s, ((cur.q / kUStages) - 1) & 1);
+        if (ok) ok = mbar_wait(a_empty + s, sp.parity ^ 1u);
+        sp.advance(kUStages);
         if (ok && warp_live) {
           tc_fence_after();
           // packed tiles arrive 128-byte swizzled: 16-byte piece p of row r sits at piece p ^ (r & 7), so the
@@ -878,7 +892,14 @@ int launch_umma(const W4Args& a, bool dependent, cudaStream_t stream) {
   UmmaPlan plan;
   plan.total_units = (a.n + 31) / 32;
   plan.ctas = plan.total_units < sm_count() ? plan.total_units : sm_count();
-  const size_t smem = kUPackedBufs * kUPackedBytes + 2 * kUXBufs * kUXBytes + 128 * a.groups * 2 + kURedBytes + 48 * sizeof(uint64_t);
+  plan.smax = 1;
+  for (int cta = 0; cta < plan.ctas; ++cta) {  // a CTA's strips: whole ones of four units, then the rest
+    const int units = static_cast<int>(static_cast<int64_t>(cta + 1) * plan.total_units / plan.ctas - static_cast<int64_t>(cta) * plan.total_units / plan.ctas);
+    if (units % 4 != 0) plan.smax = max(plan.smax, umma_split(units % 4, a.k, kUStepK));
+  }
+  plan.xdepth = 8 / plan.smax < kUMaxXBufs ? 8 / plan.smax : kUMaxXBufs;
+  plan.stages = plan.smax <= 2 ? kUMaxStages : 2;  // 16 smax accumulator columns per issuer must fit beside the stages
+  const size_t smem = kUPackedBufs * kUPackedBytes + 2 * kUXRegion + 128 * a.groups * 2 + kURedBytes + 48 * sizeof(uint64_t);
   if (smem > 225 * 1024) return XDK_ERR_LIMIT;
   CUtensorMap wmap, smap, xmap;
   {
