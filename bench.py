@@ -642,9 +642,9 @@ def main() -> None:
         for exchange, dependent in modes:
             chain_rows.append(kernel_bench.bench_chain(rank=rank, world=world, peak=peaks["hbm_gbs"], exchange=exchange,
                                                        dependent=dependent, check=chain_gate(rank, world)))
-        if world == 1:  # the layer with the two ops that follow the path: attention over the cache, SwiGLU
-            chain_rows.append(kernel_bench.bench_chain(peak=peaks["hbm_gbs"], dependent=True, attention=True,
-                                                       check=chain_gate(rank, world)))
+        if world == 1 or args.exchange == "peer":  # the layer with the two ops that follow the path: attention over the cache, SwiGLU
+            chain_rows.append(kernel_bench.bench_chain(rank=rank, world=world, peak=peaks["hbm_gbs"], exchange="peer", dependent=True,
+                                                       attention=True, check=chain_gate(rank, world)))
         mark("chain done")
 
     faults = _native.fault_flags() | (arena.fault_flags() << 0 if arena is not None else 0)
@@ -705,11 +705,16 @@ def chain_gate(rank: int, world: int):
             got = out["qkv"].cpu().double()
             _need(bool(((got - ref).abs() <= 0.002 + 0.002 * ref.abs()).all()), "chain: QKV projection outside its gate")
         else:
-            whole = DecodeLayerChain(c, layers=len(chain.layers), rank=0, world=1, seed=0, dependent_launch=False)
+            whole = DecodeLayerChain(c, layers=len(chain.layers), rank=0, world=1, seed=0, dependent_launch=False,
+                                     attention=chain.attention)
             ref = whole.run_layers()
             torch.cuda.synchronize()
-            _need(_rel_l2(out["attn"].float(), ref["attn"].float()) <= 2e-3, f"chain rank {rank}: assembled rotated Q differs from the unsharded run")
-            _need(_rel_l2(out["up_all"].float(), ref["up_all"].float()) <= 2e-3, f"chain rank {rank}: assembled up+gate differs from the unsharded run")
+            what = "attention output" if chain.attention else "rotated Q"
+            _need(_rel_l2(out["attn"].float(), ref["attn"].float()) <= 2e-3, f"chain rank {rank}: assembled {what} differs from the unsharded run")
+            if chain.attention:
+                _need(_rel_l2(out["act"].float(), ref["act"].float()) <= 3e-3, f"chain rank {rank}: assembled activation differs from the unsharded run")
+            else:
+                _need(_rel_l2(out["up_all"].float(), ref["up_all"].float()) <= 2e-3, f"chain rank {rank}: assembled up+gate differs from the unsharded run")
     return check
 
 

@@ -41,6 +41,8 @@ SIGNATURES = {
     "xdk_w4a16_v2": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _uint, _p]),
     "xdk_paged_decode_attention": (_int, [_p] * 7 + [_i64] * 6 + [_int, ctypes.c_float, _i64, _int, _uint, _p]),
     "xdk_swiglu": (_int, [_p, _p, _i64, _i64, _i64, _i64, _int, _uint, _p]),
+    "xdk_paged_decode_attention_peer": (_int, [_p] * 7 + [_i64] * 6 + [_int, ctypes.c_float, _i64, _int, _uint, _p]),
+    "xdk_swiglu_peer": (_int, [_p, _p, _i64, _i64, _i64, _int, _uint, _p]),
     "xdk_quantize_int4": (_int, [_p, _int, _i64, _i64, _int, _p, _p, _p, _p]),
     "xdk_peer_fault_flags": (ctypes.c_uint, []),
     "xdk_peer_alloc": (_int, [ctypes.c_size_t, _p]),

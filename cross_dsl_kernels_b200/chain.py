@@ -87,8 +87,13 @@ def qkv_shard_rows(cfg: ChainConfig, rank: int, world: int) -> torch.Tensor:
                       torch.arange(v0 + rank * hkv * d, v0 + (rank + 1) * hkv * d)])
 
 
-def upgate_shard_rows(cfg: ChainConfig, rank: int, world: int) -> torch.Tensor:
-    """Rows (output columns) of the up+gate weight that rank ``rank`` owns: one contiguous block."""
+def upgate_shard_rows(cfg: ChainConfig, rank: int, world: int, paired: bool = False) -> torch.Tensor:
+    """Rows (output columns) of the up+gate weight that rank ``rank`` owns.  Plain: one contiguous block of the
+    [up | gate] matrix.  ``paired`` (the layer applies SwiGLU): the rank's block of up columns followed by the same
+    block of gate columns, so that the activation of those columns needs nothing from another rank."""
+    if paired:
+        cols = cfg.mlp // world
+        return torch.cat([torch.arange(rank * cols, (rank + 1) * cols), torch.arange(cfg.mlp + rank * cols, cfg.mlp + (rank + 1) * cols)])
     cols = 2 * cfg.mlp // world
     return torch.arange(rank * cols, (rank + 1) * cols)
 
@@ -127,8 +132,8 @@ class DecodeLayerChain:
             raise ValueError("heads and MLP columns must divide by the number of ranks")
         if exchange not in ("peer", "nccl"):
             raise ValueError("exchange must be 'peer' or 'nccl'")
-        if attention and world > 1:
-            raise ValueError("the attention read is built for the single-GPU chain only")
+        if attention and world > 1 and exchange != "peer":
+            raise ValueError("the sharded chain with attention exchanges through peer-mapped stores only")
         self.cfg, self.rank, self.world, self.pg = cfg, rank, world, group
         self.exchange, self.dependent = exchange, bool(dependent_launch)
         self.attention = bool(attention)
@@ -148,7 +153,7 @@ class DecodeLayerChain:
             qkv_p, qkv_s = _quantised(c.qkv_cols, c.hidden, c.group, wgen)
             up_p, up_s = _quantised(2 * c.mlp, c.hidden, c.group, wgen)
             rows = qkv_shard_rows(c, rank, world).to(self.device)
-            up_rows = upgate_shard_rows(c, rank, world).to(self.device)
+            up_rows = upgate_shard_rows(c, rank, world, paired=attention and world > 1).to(self.device)
             layer = dict(
                 w1=w1.to(self.device), w2=w2.to(self.device),
                 qkv_packed=qkv_p[rows].contiguous(), qkv_scales=qkv_s[rows].contiguous(),
@@ -179,10 +184,12 @@ class DecodeLayerChain:
             # next layer never stores into a matrix a slower rank is still reading
             nbytes = 2 * (c.tokens * c.hidden + c.tokens * 2 * c.mlp) * 2 + 4096
             self.arena = PeerArena(nbytes, group=group, device=self.device)
+            # with attention: the attention output (sharded by KV head) and the activation (sharded by MLP column) are
+            # what the ranks assemble for one another; without it, rotated Q and the up+gate projection
             self.q_peer = [self.arena.matrix(c.tokens, c.hidden, torch.float16) for _ in range(2)]
-            self.up_peer = [self.arena.matrix(c.tokens, 2 * c.mlp, torch.float16) for _ in range(2)]
+            self.up_peer = [self.arena.matrix(c.tokens, c.mlp if attention else 2 * c.mlp, torch.float16) for _ in range(2)]
             self.site_q, self.site_up = self.arena.new_site(), self.arena.new_site()
-            self.launches_per_layer = 7  # five kernels + two flag barriers
+            self.launches_per_layer = 9 if attention else 7  # the kernels + two flag barriers
         elif world > 1:
             self.q_gather = torch.empty(world, c.tokens, hq * d, dtype=torch.float16, device=self.device)
             self.up_gather = torch.empty(world, c.tokens, 2 * c.mlp // world, dtype=torch.float16, device=self.device)
@@ -212,11 +219,21 @@ class DecodeLayerChain:
         k = qkv[:, hq * d: (hq + hkv) * d].view(c.tokens, hkv, d)
         v = qkv[:, (hq + hkv) * d:].view(c.tokens, hkv, d)
         q_dst = self.q_peer[layer % 2] if peer else None
+        sharded_attention = peer and self.attention
         q_rot = rope_gqa_paged_kv_append(q, k, v, dv["cos"], dv["sin"], dv["positions"], dv["page_table"],
                                          dv["sequence_ids"], self.k_cache, self.v_cache, page_size=c.page_size,
                                          rope_dim=d, interleaved=False, kv_layout="NHD", dependent_launch=dep,
-                                         q_peer_out=q_dst.out_for(self.rank * hq * d) if peer else None)
-        if peer:
+                                         q_peer_out=q_dst.out_for(self.rank * hq * d) if peer and not sharded_attention else None)
+        if sharded_attention:
+            from .ops import paged_decode_attention
+
+            # this rank's heads against its own cache shard; every rank receives the result
+            paged_decode_attention(q_rot, self.k_cache, self.v_cache, dv["positions"], dv["page_table"], dv["sequence_ids"],
+                                   page_size=c.page_size, context_hint=c.context, dependent_launch=dep,
+                                   peer_out=q_dst.out_for(self.rank * hq * d))
+            self.arena.barrier(self.site_q, dependent_launch=dep)
+            attn = q_dst.local
+        elif peer:
             self.arena.barrier(self.site_q, dependent_launch=dep)
             attn = q_dst.local
         elif self.world > 1:
@@ -230,6 +247,14 @@ class DecodeLayerChain:
         else:
             attn = q_rot.view(c.tokens, c.hidden)
         n2, r2 = fused_residual_rmsnorm(attn, r1, L["w2"], c.eps, dependent_launch=dep)
+        if sharded_attention:
+            from .ops import swiglu
+
+            act_dst = self.up_peer[layer % 2]
+            up = w4a16_linear(n2, L["up_packed"], L["up_scales"], None, group_size=c.group, dependent_launch=dep)  # [up_r | gate_r]
+            swiglu(up, dependent_launch=dep, peer_out=act_dst.out_for(self.rank * (c.mlp // self.world)))
+            self.arena.barrier(self.site_up, dependent_launch=dep)
+            return dict(n1=n1, r1=r1, qkv=qkv, q_rot=q_rot, attn=attn, n2=n2, r2=r2, up=up, up_all=None, act=act_dst.local)
         if peer:
             up_dst = self.up_peer[layer % 2]
             w4a16_linear(n2, L["up_packed"], L["up_scales"], None, group_size=c.group, dependent_launch=dep,

@@ -68,7 +68,7 @@ struct StageV {  // whether a warp's V rows are staged in shared memory beside i
 template <typename T, int G, int D>
 __global__ void __launch_bounds__(kAttnThreads)
 paged_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
-                              T* __restrict__ out, AttnArgs a, int splits) {
+                              const PeerOut out, AttnArgs a, int splits) {
   constexpr int E = 16 / sizeof(T);   // elements per 16-byte piece
   constexpr int PIECES = D / E;       // pieces per row
   constexpr int DPL = D / 32;         // dims per lane in the value phase
@@ -289,21 +289,21 @@ paged_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_c
           merge_stats(mm, ll, sa, sb, mr, lr);
           aa = aa * sa + ar * sb;
         }
-        out[(static_cast<int64_t>(token) * a.q_heads + kvh * G + g) * D + d] = Elem<T>::from_f32(aa / ll);
+        peer_store(out, token, (kvh * G + g) * D + d, Elem<T>::from_f32(aa / ll));
       }
     }
     cluster.sync();  // nobody leaves while rank 0 may still read its shared memory
   } else {
     for (int i = threadIdx.x; i < G * D; i += kAttnThreads) {
       const int g = i / D, d = i - g * D;
-      out[(static_cast<int64_t>(token) * a.q_heads + kvh * G + g) * D + d] = Elem<T>::from_f32(part_acc[0][g][d] / cta_l[g]);
+      peer_store(out, token, (kvh * G + g) * D + d, Elem<T>::from_f32(part_acc[0][g][d] / cta_l[g]));
     }
   }
 }
 
 // launch_opts puts the cluster along y; this kernel's cluster runs along x (the context splits)
 template <typename T, int G, int D>
-int launch_attention_cluster(const void* q, const void* kc, const void* vc, void* out, const AttnArgs& a, int64_t tokens,
+int launch_attention_cluster(const void* q, const void* kc, const void* vc, const PeerOut& out, const AttnArgs& a, int64_t tokens,
                              int splits, cudaStream_t s) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(splits), static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(tokens));
@@ -335,11 +335,11 @@ int launch_attention_cluster(const void* q, const void* kc, const void* vc, void
   cfg.attrs = attr;
   cfg.numAttrs = n;
   return note_launch(cudaLaunchKernelEx(&cfg, paged_decode_attention_kernel<T, G, D>, static_cast<const T*>(q),
-                                        static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), a, splits));
+                                        static_cast<const T*>(kc), static_cast<const T*>(vc), out, a, splits));
 }
 
 template <typename T, int G>
-int dispatch_dim(int64_t d, const void* q, const void* kc, const void* vc, void* out, const AttnArgs& a, int64_t tokens, int splits,
+int dispatch_dim(int64_t d, const void* q, const void* kc, const void* vc, const PeerOut& out, const AttnArgs& a, int64_t tokens, int splits,
                  cudaStream_t s) {
   switch (d) {
     case 64: return launch_attention_cluster<T, G, 64>(q, kc, vc, out, a, tokens, splits, s);
@@ -350,7 +350,7 @@ int dispatch_dim(int64_t d, const void* q, const void* kc, const void* vc, void*
 }
 
 template <typename T>
-int dispatch_group(int g, int64_t d, const void* q, const void* kc, const void* vc, void* out, const AttnArgs& a, int64_t tokens,
+int dispatch_group(int g, int64_t d, const void* q, const void* kc, const void* vc, const PeerOut& out, const AttnArgs& a, int64_t tokens,
                    int splits, cudaStream_t s) {
   switch (g) {
     case 1: return dispatch_dim<T, 1>(d, q, kc, vc, out, a, tokens, splits, s);
@@ -369,10 +369,26 @@ extern "C" int xdk_paged_decode_attention(const void* q, const void* k_cache, co
                                           int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t max_pages_per_seq,
                                           int64_t page_size, int cache_is_hnd, float scale, int64_t context_hint, int dtype,
                                           unsigned flags, void* stream) {
+  if (!out) return XDK_ERR_ARG;
+  xdk_peer_out one = {};
+  one.ptr[0] = out, one.world = 1, one.ld = q_heads * head_dim, one.col0 = 0;
+  return xdk_paged_decode_attention_peer(q, k_cache, v_cache, positions, page_table, sequence_ids, &one, tokens, q_heads, kv_heads,
+                                         head_dim, max_pages_per_seq, page_size, cache_is_hnd, scale, context_hint, dtype, flags,
+                                         stream);
+}
+
+extern "C" int xdk_paged_decode_attention_peer(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions,
+                                               const int64_t* page_table, const int64_t* sequence_ids, const xdk_peer_out* out_dst,
+                                               int64_t tokens, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                               int64_t max_pages_per_seq, int64_t page_size, int cache_is_hnd, float scale,
+                                               int64_t context_hint, int dtype, unsigned flags, void* stream) {
   using namespace xdk;
+  PeerOut out;
+  if (int st = make_out(out_dst, nullptr, 1, &out)) return st;
+  if (q_heads > 0 && head_dim > 0 && out.ld < out.col0 + q_heads * head_dim) return XDK_ERR_ARG;
   if (flags & ~XDK_DEPENDENT_LAUNCH) return XDK_ERR_ARG;
   CallFlagsScope scope(flags);
-  if (!q || !k_cache || !v_cache || !positions || !page_table || !sequence_ids || !out) return XDK_ERR_ARG;
+  if (!q || !k_cache || !v_cache || !positions || !page_table || !sequence_ids) return XDK_ERR_ARG;
   if (tokens < 1 || q_heads < 1 || kv_heads < 1 || head_dim < 1 || max_pages_per_seq < 1 || page_size < 1) return XDK_ERR_ARG;
   if (q_heads % kv_heads != 0 || !(scale == scale)) return XDK_ERR_ARG;
   if (tokens > 65535 || kv_heads > 65535) return XDK_ERR_LIMIT;

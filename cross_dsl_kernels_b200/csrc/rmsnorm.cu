@@ -43,13 +43,24 @@ rmsnorm_row_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
   constexpr int E = Elem<T>::kPerVec;
   __shared__ float scratch[THREADS / 32 + 1];
   pdl_launch_dependents();
+  const U4* wv = reinterpret_cast<const U4*>(weight);
+  // Short rows (few vectors per thread) fetch the weight first: it is a constant operand, so the load may start
+  // before the wait on the preceding kernel and is in flight during the reduction instead of after it.
+  constexpr bool kEarlyWeight = VPT <= 4;
+  U4 win[kEarlyWeight ? VPT : 1];
+  if constexpr (kEarlyWeight) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nvec) win[i] = ld_cached16(wv + v);
+    }
+  }
   pdl_wait();  // x and residual may be the preceding kernel's output
   const size_t row_off = static_cast<size_t>(blockIdx.x) * nvec;  // in 16-byte vectors
   const U4* xv = reinterpret_cast<const U4*>(x) + row_off;
   const U4* rv = reinterpret_cast<const U4*>(residual) + row_off;
   U4* yv = reinterpret_cast<U4*>(y) + row_off;
   U4* ov = reinterpret_cast<U4*>(residual_out) + row_off;
-  const U4* wv = reinterpret_cast<const U4*>(weight);
 
   U4 xin[VPT], rin[VPT];
 #pragma unroll
@@ -83,7 +94,8 @@ rmsnorm_row_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
     const int v = threadIdx.x + i * THREADS;
     if (v < nvec) {
       float w[E], out[E];
-      unpack16<T>(ld_cached16(wv + v), w);
+      if constexpr (kEarlyWeight) unpack16<T>(win[i], w);
+      else unpack16<T>(ld_cached16(wv + v), w);
 #pragma unroll
       for (int e = 0; e < E; ++e) out[e] = __fmul_rn(__fmul_rn(r[i][e], scale), w[e]);
       st_stream16(yv + v, pack16<T>(out));

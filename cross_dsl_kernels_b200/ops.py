@@ -18,6 +18,7 @@ without synchronising, and are safe under CUDA-graph capture.
 
 from __future__ import annotations
 
+import ctypes
 import math
 
 import torch
@@ -199,10 +200,15 @@ def rope_gqa_paged_kv_append(q, k, v, cos, sin, positions, page_table, sequence_
 
 
 def paged_decode_attention(q, k_cache, v_cache, positions, page_table, sequence_ids, *, page_size: int,
-                           kv_layout: str = "NHD", scale=None, context_hint: int = 0, dependent_launch: bool = False):
+                           kv_layout: str = "NHD", scale=None, context_hint: int = 0, dependent_launch: bool = False,
+                           peer_out=None):
     """Decode attention of one query token per sequence over the paged K/V cache that
     :func:`rope_gqa_paged_kv_append` wrote (the token's own K/V included): FP32 softmax(scale * q.K) . V per head,
-    GQA with q_heads / kv_heads in {1, 2, 4, 8}, head_dim in {64, 128, 256}.  Not part of upstream."""
+    GQA with q_heads / kv_heads in {1, 2, 4, 8}, head_dim in {64, 128, 256}.  Not part of upstream.
+
+    ``peer_out`` (multi-GPU; :meth:`cross_dsl_kernels_b200.peer.PeerMatrix.out_for`): the result goes to columns
+    [col0, col0 + q_heads * head_dim) of every rank's copy of a [tokens, all heads * head_dim] matrix instead of a
+    fresh tensor, and the call returns None; readers wait for the arena's flag barrier."""
     _gate(q)
     dtype = q.dtype
     _need(dtype in _RMS_DTYPES, "q must be float32, bfloat16 or float16")
@@ -227,19 +233,25 @@ def paged_decode_attention(q, k_cache, v_cache, positions, page_table, sequence_
     scale = float(head_dim) ** -0.5 if scale is None else float(scale)
     _need(math.isfinite(scale), "scale must be finite")
     with torch.cuda.device(q.device):
-        out = torch.empty_like(q)
-        status = _native.lib().xdk_paged_decode_attention(
-            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), page_table.data_ptr(),
-            sequence_ids.data_ptr(), out.data_ptr(), tokens, q_heads, kv_heads, head_dim, page_table.shape[1], page_size,
-            int(layout == "HND"), scale, int(context_hint), _native.dtype_code(dtype), _flags(dependent_launch),
-            _native.stream_ptr(q.device))
+        tail = (tokens, q_heads, kv_heads, head_dim, page_table.shape[1], page_size, int(layout == "HND"), scale,
+                int(context_hint), _native.dtype_code(dtype), _flags(dependent_launch), _native.stream_ptr(q.device))
+        head = (q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), page_table.data_ptr(),
+                sequence_ids.data_ptr())
+        if peer_out is None:
+            out = torch.empty_like(q)
+            status = _native.lib().xdk_paged_decode_attention(*head, out.data_ptr(), *tail)
+        else:
+            _need(peer_out.ld >= peer_out.col0 + q_heads * head_dim, "peer_out is narrower than col0 + q_heads * head_dim")
+            out = None
+            status = _native.lib().xdk_paged_decode_attention_peer(*head, ctypes.byref(peer_out), *tail)
     _native.check(status, "xdk_paged_decode_attention")
     return out
 
 
-def swiglu(upgate, *, dependent_launch: bool = False):
+def swiglu(upgate, *, dependent_launch: bool = False, peer_out=None):
     """silu(gate) * up for a fused projection output ``[rows, 2 * width]`` laid out [up | gate]; returns [rows, width].
-    Rows may be a fixed number of elements apart (a column slice of a wider matrix).  Not part of upstream."""
+    Rows may be a fixed number of elements apart (a column slice of a wider matrix).  Not part of upstream.
+    ``peer_out``: as for :func:`paged_decode_attention` (columns [col0, col0 + width) of every rank's matrix)."""
     _gate(upgate)
     _need(upgate.dtype in _RMS_DTYPES, "upgate must be float32, bfloat16 or float16")
     _need(upgate.dim() == 2 and upgate.shape[1] % 2 == 0 and upgate.shape[0] > 0 and upgate.shape[1] > 0,
@@ -247,10 +259,17 @@ def swiglu(upgate, *, dependent_launch: bool = False):
     _need(upgate.stride(1) == 1 and upgate.stride(0) >= upgate.shape[1], "upgate rows must be dense")
     rows, width = upgate.shape[0], upgate.shape[1] // 2
     with torch.cuda.device(upgate.device):
-        out = torch.empty((rows, width), dtype=upgate.dtype, device=upgate.device)
-        status = _native.lib().xdk_swiglu(upgate.data_ptr(), out.data_ptr(), rows, width,
-                                          upgate.stride(0) if rows > 1 else 2 * width, width,
-                                          _native.dtype_code(upgate.dtype), _flags(dependent_launch),
-                                          _native.stream_ptr(upgate.device))
+        in_ld = upgate.stride(0) if rows > 1 else 2 * width
+        if peer_out is None:
+            out = torch.empty((rows, width), dtype=upgate.dtype, device=upgate.device)
+            status = _native.lib().xdk_swiglu(upgate.data_ptr(), out.data_ptr(), rows, width, in_ld, width,
+                                              _native.dtype_code(upgate.dtype), _flags(dependent_launch),
+                                              _native.stream_ptr(upgate.device))
+        else:
+            _need(peer_out.ld >= peer_out.col0 + width, "peer_out is narrower than col0 + width")
+            out = None
+            status = _native.lib().xdk_swiglu_peer(upgate.data_ptr(), ctypes.byref(peer_out), rows, width, in_ld,
+                                                   _native.dtype_code(upgate.dtype), _flags(dependent_launch),
+                                                   _native.stream_ptr(upgate.device))
     _native.check(status, "xdk_swiglu")
     return out

@@ -131,12 +131,13 @@ XDK_API int xdk_rmsnorm_v2(const void* x, const void* residual, const void* weig
  * order inside one launch (thread-block cluster, distributed shared memory);
  * bias is added once, after the reduction.  Those kernels accumulate with FP32 FMAs.
  * split_k = 0 lets the library pick, and for 4 < M <= 16 the choice depends on `scratch`:
- *   scratch == NULL: a large projection (K % 64 == 0, K <= 16384, 16-byte aligned x and w, N % 4 == 0
- *     for KN weights, K*N >= 4M) runs on the tensor cores: every operand is split into two TF32 numbers and
+ *   scratch == NULL: a large projection (K % 64 == 0, K <= 16384 and, above 4096, divisible into 2, 4 or 8
+ *     parts of at most 4096 that are multiples of 64; 16-byte aligned x and w, N % 4 == 0 for KN weights,
+ *     K*N >= 4M) runs on the tensor cores: every operand is split into two TF32 numbers and
  *     the product formed as hi*hi + hi*lo + lo*hi with FP32 accumulation.  Against an FP64 product
- *     the relative L2 error is ~2e-6 at K = 4096 and below the projection's gate (1e-5) for every K the
- *     path takes (longer rows stay on FP32 FMAs), but it is not the FP32-FMA result bit for bit, and an
- *     infinity in x or W yields NaN where FP32 FMAs yield an infinity (lo = v - hi is NaN for v = inf).
+ *     the relative L2 error is ~3e-6 (8e-6 on all-positive operands), below the projection's gate (1e-5), for
+ *     every K the path takes (other rows stay on FP32 FMAs), but it is not the FP32-FMA result bit for bit, and
+ *     an infinity in x or W yields NaN where FP32 FMAs yield an infinity (lo = v - hi is NaN for v = inf).
  *     Other shapes use the cluster kernels.
  *   scratch != NULL (device memory, >= xdk_gemv_scratch_bytes(...), 16-byte aligned, written and
  *     read inside the call only -- no initialisation, no state): strict FP32 FMA arithmetic on a
@@ -265,6 +266,21 @@ XDK_API int xdk_paged_decode_attention(const void* q, const void* k_cache, const
                                unsigned flags, void* stream);
 XDK_API int xdk_swiglu(const void* upgate, void* out, int64_t rows, int64_t width, int64_t in_ld, int64_t out_ld, int dtype,
                unsigned flags, void* stream);
+/*
+ * The same two ops with the result stored into the same place of every rank's peer-mapped matrix (see
+ * xdk_gemv_f32_peer): out_dst->ld is the row pitch of the full-width matrix in elements, out_dst->col0 the first
+ * column of this rank's share ([tokens, q_heads * head_dim] for the attention output, [rows, width] for SwiGLU).
+ * A decode layer sharded by KV head (attention) and by MLP column (up and gate shards side by side on a rank)
+ * needs no other exchange than these two stores and a flag barrier after each.
+ */
+XDK_API int xdk_paged_decode_attention_peer(const void* q, const void* k_cache, const void* v_cache, const int64_t* positions,
+                                    const int64_t* page_table, const int64_t* sequence_ids, const xdk_peer_out* out_dst,
+                                    int64_t tokens, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                    int64_t max_pages_per_seq, int64_t page_size, int cache_is_hnd, float scale,
+                                    int64_t context_hint, int dtype, unsigned flags, void* stream);
+XDK_API int xdk_swiglu_peer(const void* upgate, const xdk_peer_out* out_dst, int64_t rows, int64_t width, int64_t in_ld,
+                    int dtype, unsigned flags, void* stream);
+
 
 /*
  * Symmetric INT4 quantisation on the device, into the format xdk_w4a16 reads: weight [n, k] row-major of

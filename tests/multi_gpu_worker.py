@@ -92,6 +92,28 @@ def main() -> int:
                 dist.barrier()
                 chain.arena.close()
 
+    # ---- 3b: the layer with the attention read and SwiGLU: attention sharded by KV head against the rank's own cache
+    # shard, up and gate columns paired on a rank, both results assembled on every rank through peer stores
+    del whole, ref
+    small = ChainConfig(context=2048)
+    whole = DecodeLayerChain(small, layers=2, rank=0, world=1, seed=0, attention=True)
+    ref = whole.run_layers()
+    torch.cuda.synchronize()
+    for dependent in (False, True):
+        chain = DecodeLayerChain(small, layers=2, rank=rank, world=world, seed=0, exchange="peer", dependent_launch=dependent,
+                                 attention=True)
+        out = chain.run_layers()
+        torch.cuda.synchronize()
+        dist.barrier()
+        assert torch.isfinite(out["attn"]).all() and torch.isfinite(out["act"]).all()
+        assert rel_l2(out["attn"].float(), ref["attn"].float()) <= 2e-3, (dependent, "attention output")
+        assert rel_l2(out["act"].float(), ref["act"].float()) <= 3e-3, (dependent, "SwiGLU activation")
+        assert rel_l2(out["n2"].float(), ref["n2"].float()) <= 2e-3, (dependent, "second norm")
+        assert chain.arena.fault_flags() == 0
+        dist.barrier()
+        chain.arena.close()
+    del whole, ref
+
     # ---- 4: a barrier nobody else joins runs out of time, reports it, and the context stays usable
     lonely = arena.new_site()
     dist.barrier()

@@ -62,3 +62,20 @@ def test_shards_partition_the_columns_for_every_world_size():
             hq, hkv = cfg.q_heads // world, cfg.kv_heads // world
             assert rows[hq * d].item() == cfg.q_heads * d + r * hkv * d
             assert rows[(hq + hkv) * d].item() == (cfg.q_heads + cfg.kv_heads) * d + r * hkv * d
+
+
+def test_paired_up_gate_shards_keep_a_column_and_its_gate_on_one_rank():
+    """For the layer that applies SwiGLU every rank owns a block of up columns and the same block of gate columns,
+    stored [up_r | gate_r]: the activation of those columns needs no other rank."""
+    cfg = ChainConfig()
+    for world in (1, 2, 4, 8):
+        width = cfg.mlp // world
+        seen = []
+        for r in range(world):
+            rows = upgate_shard_rows(cfg, r, world, paired=True)
+            assert rows.numel() == 2 * width
+            up, gate = rows[:width], rows[width:]
+            assert torch.equal(gate, up + cfg.mlp), "row j of the gate half gates row j of the up half"
+            assert up[0].item() == r * width and up[-1].item() == (r + 1) * width - 1
+            seen += rows.tolist()
+        assert sorted(seen) == list(range(2 * cfg.mlp))
