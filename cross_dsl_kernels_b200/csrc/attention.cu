@@ -301,6 +301,224 @@ paged_decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_c
   }
 }
 
+// ---- the same kernel with both contractions on the tensor cores (16-bit caches) --------------------------------
+// The lane-per-position kernel above spends ~1700 warp instructions per tile of 32 positions (two FMAs per cache
+// element and G heads) and is issue-bound at ~0.6 of the HBM rate.  Here the G query heads of the group are the
+// (zero-padded) 16 rows of mma.m16n8k16 tiles: S = Q K^T with K rows as the "col" operand straight from the staged
+// tile (ldmatrix), P V with V through ldmatrix.trans, P rounded to the cache type, FP32 accumulators in registers.
+// Everything else (staging, online softmax per head, merges) is as above.
+template <typename T> struct Mma16816;
+template <> struct Mma16816<__half> {
+  // rows 8-15 of A are zero, so rows 8-15 of the result are not kept: two accumulator registers per tile, not four
+  __device__ static __forceinline__ void run(float (&d)[2], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float unused2, unused3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
+                 : "+f"(d[0]), "+f"(d[1]), "=f"(unused2), "=f"(unused3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+  }
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+template <> struct Mma16816<__nv_bfloat16> {
+  __device__ static __forceinline__ void run(float (&d)[2], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float unused2, unused3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
+                 : "+f"(d[0]), "+f"(d[1]), "=f"(unused2), "=f"(unused3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+  }
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
+
+template <typename T, int G, int D>
+__global__ void __launch_bounds__(kAttnThreads, D <= 128 ? 3 : 1)
+paged_decode_attention_tc_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                                 const PeerOut out, AttnArgs a, int splits) {
+  static_assert(sizeof(T) == 2 && G <= 8 && D % 32 == 0, "16-bit caches, at most eight heads per group");
+  constexpr int PIECES = D / 8;                 // 16-byte pieces per row
+  constexpr int kPitch = D * 2 + 16;            // bytes; the pad keeps the eight rows of an ldmatrix on eight bank groups
+  constexpr int kWarpTile = 2 * 32 * kPitch;    // K rows, then V rows
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  unsigned char* ktile = attn_smem + warp_of(threadIdx.x) * kWarpTile;
+  unsigned char* vtile = ktile + 32 * kPitch;
+  float (*part_acc)[G][D] = reinterpret_cast<float (*)[G][D]>(attn_smem);
+  __shared__ int64_t rows[kAttnWarps][32];
+  __shared__ float part_m[kAttnWarps][G], part_l[kAttnWarps][G];
+  __shared__ float cta_m[G], cta_l[G];
+
+  pdl_launch_dependents();
+  pdl_wait();  // q and the caches are the preceding kernels' output
+  const int split = blockIdx.x, kvh = blockIdx.y, token = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grow = lane >> 2, quad = lane & 3;  // fragment row (= head of the group when < G), position inside the quad
+  const bool head_live = grow < G;
+  const int64_t ctx = a.positions[token] + 1;
+  const int64_t seq = a.sequence_ids[token];
+  const int64_t* table = a.page_table + seq * a.max_pages;
+  const int64_t tiles = (ctx + kAttnThreads - 1) / kAttnThreads;
+  const int64_t t0 = tiles * split / splits, t1 = tiles * (split + 1) / splits;
+
+  // Q as A fragments: a0 = (row grow, dims 16 ks + 2 quad + {0,1}), a2 = the same + 8 dims; rows >= G are zero
+  uint32_t qa0[D / 16], qa2[D / 16];
+  {
+    const T* qrow = q + (static_cast<int64_t>(token) * a.q_heads + kvh * G + (head_live ? grow : 0)) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qa0[ks] = head_live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + quad * 2) : 0u;
+      qa2[ks] = head_live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + quad * 2 + 8) : 0u;
+    }
+  }
+  float m_run = -INFINITY, l_run = 0.0f;  // of head grow; l_run is this thread's share of the sum
+  float o[D / 8][2];
+#pragma unroll
+  for (int nd = 0; nd < D / 8; ++nd) o[nd][0] = o[nd][1] = 0.0f;
+
+  for (int64_t tile = t0; tile < t1; ++tile) {
+    const int64_t base = tile * kAttnThreads + warp * 32;
+    {
+      const int64_t j = base + lane;
+      int64_t row = 0;
+      if (j < ctx) {
+        const int64_t logical = j / a.page_size, off = j - logical * a.page_size;
+        const int64_t page = __ldg(table + logical);
+        row = a.hnd ? ((page * a.kv_heads + kvh) * a.page_size + off) * D : ((page * a.page_size + off) * a.kv_heads + kvh) * D;
+      }
+      rows[warp][lane] = row;  // dead positions point at row 0: a valid address, and their probability is 0
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < PIECES; ++i) {
+      const int c = i * 32 + lane, r = c / PIECES, p = c - r * PIECES;
+      cp_async16(ktile + r * kPitch + p * 16, reinterpret_cast<const unsigned char*>(k_cache + rows[warp][r]) + p * 16);
+    }
+#pragma unroll
+    for (int i = 0; i < PIECES; ++i) {
+      const int c = i * 32 + lane, r = c / PIECES, p = c - r * PIECES;
+      cp_async16(vtile + r * kPitch + p * 16, reinterpret_cast<const unsigned char*>(v_cache + rows[warp][r]) + p * 16);
+    }
+    cp_async_wait_all();
+    __syncwarp();
+
+    // ---- S = Q K^T: four n-tiles of eight positions; lane supplies the address of row (lane % 8) of matrix lane / 8
+    float sc[4][2];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      sc[nt][0] = sc[nt][1] = 0.0f;
+      const unsigned char* krow = ktile + (nt * 8 + (lane & 7)) * kPitch + (lane >> 3) * 16;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ks += 2) {  // one ldmatrix.x4 = the (b0, b1) of two k slices
+        uint32_t b[4];
+        ldmatrix_x4(b, krow + ks * 32);
+        Mma16816<T>::run(sc[nt], qa0[ks], qa2[ks], b[0], b[1]);
+        Mma16816<T>::run(sc[nt], qa0[ks + 1], qa2[ks + 1], b[2], b[3]);
+      }
+    }
+    // ---- online softmax of head grow: this thread holds positions base + 8 nt + 2 quad + {0, 1}
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const bool live = base + nt * 8 + quad * 2 + e < ctx;
+        sc[nt][e] = live ? sc[nt][e] * a.scale : -INFINITY;
+        mx = fmaxf(mx, sc[nt][e]);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float corr = m_run == -INFINITY ? 0.0f : __expf(m_run - m_new);
+    uint32_t pa[4];  // P as A fragments: k slice kp = positions 16 kp .. 16 kp + 15: a0 from n-tile 2 kp, a2 from 2 kp + 1
+    float psum = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const float p0 = sc[nt][0] == -INFINITY ? 0.0f : __expf(sc[nt][0] - m_new);
+      const float p1 = sc[nt][1] == -INFINITY ? 0.0f : __expf(sc[nt][1] - m_new);
+      psum += p0 + p1;
+      pa[nt] = Mma16816<T>::pack(p0, p1);
+    }
+    l_run = l_run * corr + psum;
+    m_run = m_new;
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd) o[nd][0] *= corr, o[nd][1] *= corr;
+    // ---- O += P V: V^T through ldmatrix.trans; matrix lane / 8 = (position half, dim tile)
+#pragma unroll
+    for (int kp = 0; kp < 2; ++kp) {
+      const unsigned char* vrow = vtile + (kp * 16 + (lane >> 3 & 1) * 8 + (lane & 7)) * kPitch + (lane >> 4) * 16;
+#pragma unroll
+      for (int nd = 0; nd < D / 8; nd += 2) {  // one ldmatrix.x4.trans = the (b0, b1) of two dim tiles
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vrow + nd * 16);
+        Mma16816<T>::run(o[nd], pa[2 * kp], pa[2 * kp + 1], b[0], b[1]);
+        Mma16816<T>::run(o[nd + 1], pa[2 * kp], pa[2 * kp + 1], b[2], b[3]);
+      }
+    }
+    __syncwarp();  // the tile's shared entries are free for the next tile
+  }
+
+  // ---- warp totals, then the four warps of the CTA (fixed order)
+  __syncthreads();  // every warp is done with its tiles: the buffer now holds the accumulators
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (head_live) {
+    if (quad == 0) part_m[warp][grow] = m_run, part_l[warp][grow] = l_run;
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd) {
+      part_acc[warp][grow][nd * 8 + quad * 2] = o[nd][0];
+      part_acc[warp][grow][nd * 8 + quad * 2 + 1] = o[nd][1];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += kAttnThreads) {
+    const int g = i / D, d = i - g * D;
+    float mm = part_m[0][g], ll = part_l[0][g], aa = part_acc[0][g][d];
+    for (int w = 1; w < kAttnWarps; ++w) {
+      float sa, sb;
+      merge_stats(mm, ll, sa, sb, part_m[w][g], part_l[w][g]);
+      aa = aa * sa + part_acc[w][g][d] * sb;
+    }
+    part_acc[0][g][d] = aa;
+    if (d == 0) cta_m[g] = mm, cta_l[g] = ll;
+  }
+  __syncthreads();
+
+  if (splits > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();  // every slice's partial is in its CTA's shared memory
+    if (split == 0) {
+      for (int i = threadIdx.x; i < G * D; i += kAttnThreads) {
+        const int g = i / D, d = i - g * D;
+        float mm = cta_m[g], ll = cta_l[g], aa = part_acc[0][g][d];
+        for (int r = 1; r < splits; ++r) {  // rank order
+          const float mr = *cluster.map_shared_rank(&cta_m[g], r), lr = *cluster.map_shared_rank(&cta_l[g], r);
+          const float ar = *cluster.map_shared_rank(&part_acc[0][g][d], r);
+          float sa, sb;
+          merge_stats(mm, ll, sa, sb, mr, lr);
+          aa = aa * sa + ar * sb;
+        }
+        peer_store(out, token, (kvh * G + g) * D + d, Elem<T>::from_f32(aa / ll));
+      }
+    }
+    cluster.sync();  // nobody leaves while rank 0 may still read its shared memory
+  } else {
+    for (int i = threadIdx.x; i < G * D; i += kAttnThreads) {
+      const int g = i / D, d = i - g * D;
+      peer_store(out, token, (kvh * G + g) * D + d, Elem<T>::from_f32(part_acc[0][g][d] / cta_l[g]));
+    }
+  }
+}
+
 // launch_opts puts the cluster along y; this kernel's cluster runs along x (the context splits)
 template <typename T, int G, int D>
 int launch_attention_cluster(const void* q, const void* kc, const void* vc, const PeerOut& out, const AttnArgs& a, int64_t tokens,
@@ -308,12 +526,16 @@ int launch_attention_cluster(const void* q, const void* kc, const void* vc, cons
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(splits), static_cast<unsigned>(a.kv_heads), static_cast<unsigned>(tokens));
   cfg.blockDim = dim3(kAttnThreads);
-  constexpr size_t tile_bytes = static_cast<size_t>(kAttnWarps) * 32 * ((StageV<T, D>::value ? 2 : 1) * D * sizeof(T) + 16);
+  constexpr bool kTensorCores = sizeof(T) == 2;  // 16-bit caches: both contractions as mma.sync tiles
+  constexpr size_t tile_bytes = kTensorCores ? static_cast<size_t>(kAttnWarps) * 2 * 32 * (D * sizeof(T) + 16)
+                                             : static_cast<size_t>(kAttnWarps) * 32 * ((StageV<T, D>::value ? 2 : 1) * D * sizeof(T) + 16);
   constexpr size_t acc_bytes = static_cast<size_t>(kAttnWarps) * G * D * sizeof(float);
   constexpr size_t smem = tile_bytes > acc_bytes ? tile_bytes : acc_bytes;
+  void (*kernel)(const T*, const T*, const T*, const PeerOut, AttnArgs, int);
+  if constexpr (kTensorCores) kernel = paged_decode_attention_tc_kernel<T, G, D>;
+  else kernel = paged_decode_attention_kernel<T, G, D>;
   if (smem > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(paged_decode_attention_kernel<T, G, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem));
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) return note_launch(err);
   }
   cfg.dynamicSmemBytes = smem;
@@ -334,8 +556,8 @@ int launch_attention_cluster(const void* q, const void* kc, const void* vc, cons
   }
   cfg.attrs = attr;
   cfg.numAttrs = n;
-  return note_launch(cudaLaunchKernelEx(&cfg, paged_decode_attention_kernel<T, G, D>, static_cast<const T*>(q),
-                                        static_cast<const T*>(kc), static_cast<const T*>(vc), out, a, splits));
+  return note_launch(cudaLaunchKernelEx(&cfg, kernel, static_cast<const T*>(q), static_cast<const T*>(kc),
+                                        static_cast<const T*>(vc), out, a, splits));
 }
 
 template <typename T, int G>
@@ -402,9 +624,13 @@ extern "C" int xdk_paged_decode_attention_peer(const void* q, const void* k_cach
   a.scale = scale;
   // Context splits: as many CTAs as the SMs hold at once, at most one split per 128-position tile of the longest
   // context the caller expects (context_hint; <= 0: assume long contexts), at most the portable cluster size.
+  // CTAs an SM holds at once, by the shared memory of the kernel that will run (registers allow four)
   const int64_t elem = dtype == XDK_F32 ? 4 : 2;
-  const bool staged = kAttnWarps * 32 * (2 * head_dim * elem + 16) <= 72 * 1024;  // StageV of the kernel that will run
-  const int64_t resident = staged ? 3 : 4;                                          // CTAs an SM holds at once
+  const bool staged = kAttnWarps * 32 * (2 * head_dim * elem + 16) <= 72 * 1024;  // StageV of the FP32 kernel
+  const int64_t tile_smem = dtype == XDK_F32 ? kAttnWarps * 32 * ((staged ? 2 : 1) * head_dim * elem + 16)
+                                            : kAttnWarps * 2 * 32 * (head_dim * elem + 16);
+  int64_t resident = (220 * 1024) / (tile_smem > 0 ? tile_smem : 1);
+  resident = resident < 1 ? 1 : (resident > 4 ? 4 : resident);
   int splits = static_cast<int>(resident * sm_count() / (tokens * kv_heads));      // one wave, never a partial second one
   if (context_hint > 0) {
     const int64_t tiles = (context_hint + kAttnThreads - 1) / kAttnThreads;
