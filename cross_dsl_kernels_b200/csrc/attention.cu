@@ -17,7 +17,9 @@
 //            memory, broadcast reads); no shuffles.
 //   softmax: per warp and head, running maximum and sum (online softmax) -- one warp max per tile and head.
 //   values : lanes turn to own dim/32 dims each; the tile's probabilities and row addresses go through shared
-//            memory (one broadcast read per position), V rows are read coalesced.
+//            memory (one broadcast read per position); the V rows were staged together with the K rows (head sizes
+//            whose tiles would leave too few CTAs per SM read them straight from global memory instead).
+// 16-bit caches take the tensor-core variant further down: same staging and merges, both contractions as mma tiles.
 // The four warps' partial (max, sum, accumulator) are merged in shared memory; the slices of one (token, KV head)
 // form a thread-block cluster and are merged in rank order through distributed shared memory, so there is no
 // scratch buffer, no second launch, and the result is deterministic.
