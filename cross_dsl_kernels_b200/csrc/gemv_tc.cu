@@ -41,6 +41,8 @@
 // division in a one-thread role 0.1 us -- and that chain, not HBM, sets the step time (a run without any W traffic
 // took as long).  A third A stage, a third x buffer, sixteen split warps and 32-column stores were each measured:
 // no gain, so two stages, two x buffers (buffer s and stage s share their "MMAs done" barrier) and eight warps.
+// The kernel's time also moves by several per cent with how the compiler schedules the roles, so the switches of
+// those comparisons (XDK_TC_MMA3, XDK_TC_NACCS, XDK_TC_ROT, XDK_TC_SLOT; defaults = the fastest measured) stayed in.
 // TMEM columns (512): accumulators first -- 64 per issuer, 32 S per accumulator (hi.hi + lo.hi | hi.lo) -- then
 // stage s at 256 + 128 s: 64 hi columns, 64 lo.
 // Every wait is time-bounded; on a timeout the kernel raises a fault word, stops issuing work, and still frees
@@ -91,6 +93,10 @@ struct TcArgs {
   int split;  // k ranges per strip (1, 2, 4), the same for every strip of the launch
   int ring;   // W step buffers
   int kparts; // CTAs of a cluster that share every strip, each walking K / kparts (1, 2, 4, 8); grid = (ctas, kparts)
+  int wide;   // 1: W_hi meets [x_hi | x_lo] in one MMA of 32 S columns (2 MMAs per k block); 0: three MMAs of 16 S
+  int max_accs;
+  int rotate;     // 1: every CTA starts its k loop at another step (no two CTAs ask L2 for the same x lines at once)
+  int tight_ring; // 1: a CTA whose strips are narrower than 128 columns cuts the ring into smaller, more slots
 };
 
 
@@ -126,7 +132,7 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int S = a.split;
   const int issuers = kMaxIssuers, acc_cols = kTmemA / issuers;
-  constexpr int acc_w = 32;  // columns of an accumulator per k range: [hi.hi + lo.hi | hi.lo]
+  const int acc_w = a.wide ? 32 : 16;  // columns of an accumulator per k range: [hi.hi + lo.hi | hi.lo] or one sum
   const int kXHalfBytes = S * kXHalf1, kXBytes = 2 * kXHalfBytes, kXRawBytes = S * kXRaw1;
   unsigned char* ring = smem_raw;                            // [a.ring][kStepBytes], re-cut below
   unsigned char* xbuf = ring + a.ring * kStepBytes;          // [kXBufs][hi image | lo image], 16 S rows each
@@ -154,7 +160,13 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
   const int k_len = a.k / a.kparts, k_base = part * k_len;
   UmmaCursor cur;
   cur.init(blockIdx.x, a.ctas, a.total_units, k_len, kStepK, S);
-  const int slot_bytes = kStepBytes, kRing = a.ring;
+  // The ring holds a.ring steps of 128 columns.  A CTA whose widest strip (its first) has fewer columns needs less
+  // per step and cuts the same bytes into more slots: more W in flight against the 3-4 us a load takes under load.
+  const int widest = min(4, cur.unit_end - cur.unit);
+  const int slot_bytes = (a.tight_ring && S == 1 && widest > 0) ? widest * kQuarterBytes : kStepBytes;
+  const int kRing = min(kMaxRing, a.ring * kStepBytes / slot_bytes);
+  // first k step of this CTA's loop over a strip (taken modulo the strip's steps)
+  const int rot_seed = a.rotate ? static_cast<int>(blockIdx.x) * 5 + part * 3 : 0;
 
   if (warp == 0) {  // one barrier per lane
     if (lane < kRing) {
@@ -203,12 +215,14 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
         const int qpk = 4 / cur.split;  // lane quarters per k range = units the strip can hold
         const bool live = lq % qpk < cur.units;
         const int col0 = (cur.unit + lq % qpk) * 32, k_range0 = (lq / qpk) * cur.kper;
+        int kk = rot_seed % cur.steps;  // the step this CTA walks now: kk, kk + 1, ..., steps - 1, 0, ...
         do {
           const int buf = w.slot;
           ok = __all_sync(0xffffffffu, mbar_wait(w_empty + buf, w.parity ^ 1u));
           if (!ok) break;
           w.advance(kRing);
-          const int k0 = k_base + k_range0 + cur.kc * kStepK;
+          const int k0 = k_base + k_range0 + kk * kStepK;
+          kk = kk + 1 == cur.steps ? 0 : kk + 1;
           if (elect_one()) {
             unsigned char* dst = ring + buf * slot_bytes + lq * kQuarterBytes;
             if (NK) {  // two [32 columns][32 k] boxes, 128-byte rows, swizzled
@@ -245,7 +259,7 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
       RingPos st;
       while (ok && cur.begin_strip()) {
         const uint32_t idesc = umma_idesc(16 * cur.split, 2u), idesc_wide = umma_idesc(32 * cur.split, 2u);
-        const int naccs = min(acc_cols / (acc_w * S), cur.steps);
+        const int naccs = min(min(acc_cols / (acc_w * S), cur.steps), a.max_accs);
         do {
           const int s = st.slot, xb = s;
           ok = __all_sync(0xffffffffu, mbar_wait(x_full + xb, st.parity) && mbar_wait(a_full + s, st.parity));
@@ -260,15 +274,22 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
           const uint32_t a_hi = tmem_base + kTmemA + s * kStageCols + issuer * 8;
           const uint32_t x_lo = xd_lo + ((xb * kXBytes + issuer * 2 * kXLbo) >> 4);
           if (elect_one()) {
-            for (int j = 0; j < nj; ++j) {
-              uint64_t b_hi;  // the hi image; the lo image follows it at the same row-group pitch: one operand of 32 S rows
-              const uint32_t off = (j * issuers * 2 * kXLbo) >> 4;
-              asm("mov.b64 %0, {%1, %2};" : "=l"(b_hi) : "r"(x_lo + off), "r"(xd_hi));
-              const uint32_t ah = a_hi + j * issuers * 8;
-              umma_tf32_ta(acc, ah, b_hi, idesc_wide, !(fresh && j == 0));  // W_hi . [x_hi | x_lo]
-              umma_tf32_ta(acc, ah + kStepK, b_hi, idesc, true);           // W_lo . x_hi onto the first half
+          for (int j = 0; j < nj; ++j) {
+            uint64_t b_hi, b_lo;
+            const uint32_t off = (j * issuers * 2 * kXLbo) >> 4;
+            asm("mov.b64 %0, {%1, %2};" : "=l"(b_hi) : "r"(x_lo + off), "r"(xd_hi));
+            asm("mov.b64 %0, {%1, %2};" : "=l"(b_lo) : "r"(x_lo + off + (kXHalfBytes >> 4)), "r"(xd_hi));
+            const uint32_t ah = a_hi + j * issuers * 8;
+            if (a.wide) {  // the lo image follows the hi image at the same row-group pitch: one operand of 32 S rows
+              umma_tf32_ta(acc, ah, b_hi, idesc_wide, !(fresh && j == 0));
+              umma_tf32_ta(acc, ah + kStepK, b_hi, idesc, true);
+            } else {
+              umma_tf32_ta(acc, ah, b_hi, idesc, !(fresh && j == 0));
+              umma_tf32_ta(acc, ah, b_lo, idesc, true);
+              umma_tf32_ta(acc, ah + kStepK, b_hi, idesc, true);
             }
-            umma_commit(mma_done + s);
+          }
+          umma_commit(mma_done + s);
           }
           __syncwarp();
         } while (cur.next_step());
@@ -284,15 +305,20 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
     UmmaCursor ahead = cur;  // issues the loads, kXBufs steps in front of `cur`
     bool ahead_live = ahead.begin_strip();
     RingPos xi, xs;          // of the load being issued, of the step being transformed
+    int xkk = ahead_live ? rot_seed % ahead.steps : 0;
     auto issue = [&]() {  // raw buffer xi.slot is free: its last readers passed the x-warp barrier
       if (!ahead_live) return;
       if (t == 0) {
         const int xb = xi.slot;
         mbar_expect_tx(x_raw + xb, static_cast<unsigned>(kXRawBytes));  // rows >= M are out of range: zero-filled, still counted
-        tma_box_4d(xraw + xb * kXRawBytes, &xmap, ahead.kc * kStepK, 0, part, 0, x_raw + xb);  // all k ranges in one box
+        tma_box_4d(xraw + xb * kXRawBytes, &xmap, xkk * kStepK, 0, part, 0, x_raw + xb);  // all k ranges in one box
       }
       xi.advance(kXBufs);
-      if (!ahead.next_step()) ahead_live = ahead.begin_strip();
+      xkk = xkk + 1 == ahead.steps ? 0 : xkk + 1;
+      if (!ahead.next_step()) {
+        ahead_live = ahead.begin_strip();
+        if (ahead_live) xkk = rot_seed % ahead.steps;
+      }
     };
     for (int i = 0; i < kXBufs; ++i) issue();
     // A quarter warp moves an 8-row x 8-k-group block along its diagonals: lane i takes k group i of row
@@ -348,7 +374,7 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
       const bool warp_live = uq < cur.units;    // warp-uniform: a quarter without columns writes nothing
       const int col = (cur.unit + uq) * 32 + lane;
       const int split = cur.split;
-      const int naccs = min(acc_cols / (acc_w * S), cur.steps);
+      const int naccs = min(min(acc_cols / (acc_w * S), cur.steps), a.max_accs);
       const int pitch = cur.units * 32;  // KN: floats per k row of the tile
       do {
         const int buf = w.slot, s = st.slot;
@@ -400,19 +426,20 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
         if (ok) ok = mbar_wait(acc_full, strip_i & 1);
         if (ok && warp_live) {
           tc_fence_after();
-          // one accumulator per round: its loads (the hi.hi + lo.hi columns and the hi.lo columns) go out together
-          // and are waited for once; fixed order of additions
+          // one accumulator per round: its loads (hi.hi + lo.hi columns, and hi.lo columns in the wide form) go out
+          // together and are waited for once; fixed order of additions
           for (int i = 0; i < issuers; ++i) {
             for (int sel = 0; sel < naccs; ++sel) {
               uint32_t r0[16], r1[16];
               const uint32_t t0 = lane_base + i * acc_cols + sel * acc_w * S + ks * 16;
               tmem_ld16_issue(t0, r0);
-              tmem_ld16_issue(t0 + 16 * S, r1);
+              if (a.wide) tmem_ld16_issue(t0 + 16 * S, r1);
               tmem_ld_wait16(r0);
-              tmem_ld_wait16(r1);
+              if (a.wide) tmem_ld_wait16(r1);
 #pragma unroll
               for (int m = 0; m < 16; ++m) {
-                const float v = __fadd_rn(__uint_as_float(r0[m]), __uint_as_float(r1[m]));
+                float v = __uint_as_float(r0[m]);
+                if (a.wide) v = __fadd_rn(v, __uint_as_float(r1[m]));
                 sum[m] = (i == 0 && sel == 0) ? v : __fadd_rn(sum[m], v);
               }
             }
@@ -525,7 +552,9 @@ size_t plan_tc(TcArgs& a, int k, int n) {
   a.total_units = (n + 31) / 32;
   const float step_us[5] = {0.0f, 0.62f, 0.85f, 0.0f, 1.3f};
   const float hbm_us = static_cast<float>(k) * static_cast<float>(n) * 4.0f / 6.0e6f;
-  constexpr int acc_w = 32;  // accumulator columns per k range
+  static const bool three = getenv("XDK_TC_MMA3") && getenv("XDK_TC_MMA3")[0] == '1';
+  a.wide = three ? 0 : 1;
+  const int acc_w = a.wide ? 32 : 16;
   const int max_split = kTmemA / kMaxIssuers / acc_w;  // an accumulator must fit an issuer's columns
   float best = 1e30f;
   a.kparts = 0, a.split = 1, a.ctas = 0;
@@ -548,6 +577,11 @@ size_t plan_tc(TcArgs& a, int k, int n) {
     }
   }
   if (a.kparts == 0) return 0;  // no admissible split of this K
+  static const int forced_accs = getenv("XDK_TC_NACCS") ? atoi(getenv("XDK_TC_NACCS")) : 0;
+  a.max_accs = forced_accs > 0 ? forced_accs : 64;
+  static const bool no_rotate = getenv("XDK_TC_ROT") && getenv("XDK_TC_ROT")[0] == '0';
+  static const bool no_tight = getenv("XDK_TC_SLOT") && getenv("XDK_TC_SLOT")[0] == '0';
+  a.rotate = no_rotate ? 0 : 1, a.tight_ring = no_tight ? 0 : 1;
   const size_t fixed = kXBufs * static_cast<size_t>(a.split) * (2 * kXHalf1 + kXRaw1) + kRedBytes * a.kparts + 64 * sizeof(uint64_t);
   a.ring = static_cast<int>((220 * 1024 - fixed) / kStepBytes);
   if (a.ring > kMaxRing) a.ring = kMaxRing;
