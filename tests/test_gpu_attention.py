@@ -110,3 +110,41 @@ def test_swiglu(dtype, rows, width):
     wide = torch.zeros(rows, 2 * width + 16, dtype=dtype)
     wide[:, : 2 * width] = x
     assert torch.equal(swiglu(wide.cuda()[:, : 2 * width]).cpu(), got), "rows a fixed number of elements apart"
+
+
+def _one_rank_out(matrix, col0):
+    """The descriptor a rank of a one-rank "arena" would pass: columns [col0, ...) of its own wider matrix."""
+    from cross_dsl_kernels_b200 import _native
+    out = _native.PeerOutStruct()
+    out.ptr[0] = matrix.data_ptr()
+    out.world, out.ld, out.col0 = 1, matrix.shape[1], col0
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_attention_and_swiglu_store_into_a_slice_of_a_wider_matrix(dtype):
+    """The peer form of both ops (a rank's heads / columns inside the full-width matrix every rank assembles), with one
+    rank: same values as the plain call, nothing written outside the slice."""
+    from cross_dsl_kernels_b200.ops import paged_decode_attention, swiglu
+    tokens, q_heads, kv_heads, dim, ps = 5, 8, 2, 128, 16
+    q, kc, vc, pos, table, seq = make_cache(tokens, q_heads, kv_heads, dim, ps, 600, "NHD", dtype, seed=3)
+    args = (q.cuda(), kc.cuda(), vc.cuda(), pos.cuda(), table.cuda(), seq.cuda())
+    plain = paged_decode_attention(*args, page_size=ps)
+    hidden = 3 * q_heads * dim  # the matrix of three such ranks; this one is the middle one
+    full = torch.full((tokens, hidden), -7.0, dtype=dtype, device="cuda")
+    assert paged_decode_attention(*args, page_size=ps, peer_out=_one_rank_out(full, q_heads * dim)) is None
+    torch.cuda.synchronize()
+    assert torch.equal(full[:, q_heads * dim: 2 * q_heads * dim], plain.view(tokens, q_heads * dim))
+    assert bool((full[:, : q_heads * dim] == -7.0).all()) and bool((full[:, 2 * q_heads * dim:] == -7.0).all())
+    with pytest.raises(ValueError):
+        paged_decode_attention(*args, page_size=ps, peer_out=_one_rank_out(full, hidden - 8))
+
+    for width in (512, 513):  # vector and scalar store paths
+        g = torch.Generator().manual_seed(width)
+        x = torch.randn(tokens, 2 * width, generator=g).to(dtype).cuda()
+        want = swiglu(x)
+        act = torch.full((tokens, 3 * width + 8), -7.0, dtype=dtype, device="cuda")
+        assert swiglu(x, peer_out=_one_rank_out(act, width)) is None
+        torch.cuda.synchronize()
+        assert torch.equal(act[:, width: 2 * width], want)
+        assert bool((act[:, :width] == -7.0).all()) and bool((act[:, 2 * width:] == -7.0).all())
