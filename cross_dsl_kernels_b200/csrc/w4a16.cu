@@ -953,6 +953,134 @@ w4a16_generic_kernel(W4Args a) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Direct-load tensor-core path for M <= 8 and K % 1024 == 0.
+//
+// The SIMT kernel spends five thread instructions per code (the exact unpack, then an FMA per code and row with
+// both operands taken out of their half2 pairs) and is issue-bound at a third of the HBM rate on this part.  Here
+// the unpack's half2 pairs go to mma.m16n8k16 as they are, with the operands swapped so that no row of the MMA is
+// wasted on small M: the 16 rows of the MMA are 16 columns of W, its 8 columns are the (up to 8) rows of x.  Lane
+// (n = lane / 4, q = lane % 4) loads the 16-byte vectors (32 codes) of columns n and n + 8 that start at
+// k = chunk + 32 q.  An MMA does not care which k a fragment slot stands for as long as A and B agree, so slot pairs
+// are simply "the pairs the unpack produces": word w of a vector gives A pairs (k0,k4) (k1,k5) for one MMA and
+// (k2,k6) (k3,k7) for the next, and the matching B pairs are one 16-byte read of x, which sits in shared memory
+// already permuted to (0,4,1,5,2,6,3,7) inside every 8 k.  (The legacy HMMA pipe of this part retires one
+// m16n8k16 per 32 cycles and sub-partition; with x as the 16-row operand -- 8 columns of W per MMA -- that pipe
+// alone took 12 us at N = 14336.)
+// A CTA is eight warps that split K eight ways over the same 16 columns (all loads of a warp's share go out before
+// the first is used: one trip to HBM per column pass) and add their partial sums in shared memory in warp order.
+__global__ void __launch_bounds__(kThreads)
+w4a16_mma_kernel(W4Args a, int passes) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int pitch = a.k * 2 + 16;                          // bytes per x row: the pad puts the 8 rows on different banks
+  unsigned char* xs = smem_raw;                            // [m rows][pitch], k permuted inside every 8
+  float* red = reinterpret_cast<float*>(smem_raw + ((static_cast<size_t>(a.m) * pitch + 127) & ~static_cast<size_t>(127)));  // [8 warps][32 lanes][4]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = lane >> 2, q = lane & 3;
+  const int row_bytes = a.k / 2;
+  const int k_warp = a.k / kWarps;          // this warp's share of K, a multiple of 128
+  const int chunks = k_warp / 128;          // 128 k per chunk: 32 per lane of a quad
+  const int k0 = warp * k_warp + q * 32;    // first k of this lane's vectors
+  const int cta_col0 = blockIdx.x * passes * 16;
+
+  // the first pass's weights go out before x is staged
+  constexpr int kMaxChunks = 4;             // chunks per round of loads (K <= 4096: one round)
+  U4 wv[kMaxChunks][2];                     // [chunk][column n, column n + 8]
+  __half sc[kMaxChunks][2];
+  auto fetch = [&](int col_base, int chunk0) {
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int col = col_base + h * 8 + n, k = k0 + (chunk0 + c) * 128;
+        wv[c][h] = U4{0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};  // code 8 == weight 0
+        sc[c][h] = __float2half(0.0f);
+        if (chunk0 + c < chunks && col < a.n) {
+          wv[c][h] = ld_stream16(a.packed + static_cast<size_t>(col) * row_bytes + k / 2);
+          sc[c][h] = __ldg(a.scales + static_cast<size_t>(col) * a.groups + k / a.group);
+        }
+      }
+  };
+  fetch(cta_col0, 0);
+
+  const int units = a.k / 8;
+  for (int i = threadIdx.x; i < a.m * units; i += kThreads) {
+    const int r = i / units, u = i - r * units;
+    const U4 v = ld_cached16(a.x + static_cast<size_t>(r) * a.k + u * 8);
+    U4 o;  // k 0..7 -> 0,4,1,5,2,6,3,7: the pairs the unpack produces
+    o.x = __byte_perm(v.x, v.z, 0x5410);
+    o.y = __byte_perm(v.x, v.z, 0x7632);
+    o.z = __byte_perm(v.y, v.w, 0x5410);
+    o.w = __byte_perm(v.y, v.w, 0x7632);
+    *reinterpret_cast<U4*>(xs + static_cast<size_t>(r) * pitch + u * 16) = o;
+  }
+  __syncthreads();
+  const bool row_live = n < a.m;  // this lane's B fragments: row n of x
+  const unsigned char* xrow = xs + static_cast<size_t>(row_live ? n : 0) * pitch;
+
+  for (int pass = 0; pass < passes; ++pass) {
+    const int col_base = cta_col0 + pass * 16;
+    if (col_base >= a.n) break;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // (column n, rows 2 q + {0, 1} of x), (column n + 8, the same rows)
+    for (int chunk0 = 0; chunk0 < chunks; chunk0 += kMaxChunks) {
+      if (chunk0 > 0) fetch(col_base, chunk0);
+#pragma unroll
+      for (int c = 0; c < kMaxChunks; ++c) {
+        if (chunk0 + c < chunks) {
+          const unsigned char* xk = xrow + (k0 + (chunk0 + c) * 128) * 2;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            U4 xv = U4{0u, 0u, 0u, 0u};
+            if (row_live) xv = *reinterpret_cast<const U4*>(xk + w * 16);
+            const uint32_t w0 = w == 0 ? wv[c][0].x : (w == 1 ? wv[c][0].y : (w == 2 ? wv[c][0].z : wv[c][0].w));
+            const uint32_t w1 = w == 0 ? wv[c][1].x : (w == 1 ? wv[c][1].y : (w == 2 ? wv[c][1].z : wv[c][1].w));
+            __half2 h0[4], h1[4];
+            dequant8(w0, __half2half2(sc[c][0]), h0);
+            dequant8(w1, __half2half2(sc[c][1]), h1);
+            mma16816(acc, *reinterpret_cast<uint32_t*>(&h0[0]), *reinterpret_cast<uint32_t*>(&h1[0]), *reinterpret_cast<uint32_t*>(&h0[1]),
+                     *reinterpret_cast<uint32_t*>(&h1[1]), xv.x, xv.y);
+            mma16816(acc, *reinterpret_cast<uint32_t*>(&h0[2]), *reinterpret_cast<uint32_t*>(&h1[2]), *reinterpret_cast<uint32_t*>(&h0[3]),
+                     *reinterpret_cast<uint32_t*>(&h1[3]), xv.z, xv.w);
+          }
+        }
+      }
+    }
+    // the next pass's first round of weights is on its way while the partial sums meet
+    if (pass + 1 < passes && col_base + 16 < a.n) fetch(col_base + 16, 0);
+    *reinterpret_cast<float4*>(red + (warp * 32 + lane) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    if (warp == 0) {  // the eight partial sums in warp order, bias, store
+      float4 total = *reinterpret_cast<const float4*>(red + lane * 4);
+      for (int w = 1; w < kWarps; ++w) {
+        const float4 part = *reinterpret_cast<const float4*>(red + (w * 32 + lane) * 4);
+        total.x = __fadd_rn(total.x, part.x), total.y = __fadd_rn(total.y, part.y);
+        total.z = __fadd_rn(total.z, part.z), total.w = __fadd_rn(total.w, part.w);
+      }
+      const float out[4] = {total.x, total.y, total.z, total.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = col_base + (e >> 1) * 8 + n, row = q * 2 + (e & 1);
+        if (row < a.m && col < a.n)
+          a.y[static_cast<size_t>(row) * a.n + col] = __float2half_rn(out[e] + (a.bias ? __half2float(a.bias[col]) : 0.0f));
+      }
+    }
+    __syncthreads();  // red is free for the next pass
+  }
+}
+
+int launch_mma(W4Args a, cudaStream_t stream) {
+  const size_t xbytes = (static_cast<size_t>(a.m) * (a.k * 2 + 16) + 127) & ~static_cast<size_t>(127);
+  const size_t smem = xbytes + static_cast<size_t>(kWarps) * 32 * 4 * sizeof(float);
+  cudaError_t err = cudaFuncSetAttribute(w4a16_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (err != cudaSuccess) return note_launch(err);
+  // columns per CTA: enough CTAs for two per SM, at least one pass of 16 columns
+  const int groups = (a.n + 15) / 16;
+  int passes = groups / (2 * sm_count());
+  if (passes < 1) passes = 1;
+  const int ctas = (groups + passes - 1) / passes;
+  return launch(w4a16_mma_kernel, dim3(ctas), dim3(kThreads), smem, stream, 1u, a, passes);
+}
+
 template <int MT, int CW>
 int launch_simt(W4Args a, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(MT) * a.k * sizeof(__half);
@@ -1030,6 +1158,14 @@ extern "C" int xdk_w4a16_peer(const void* x, const uint8_t* packed, const void* 
   static const int umma_env = getenv("XDK_W4A16_UMMA") ? (getenv("XDK_W4A16_UMMA")[0] == '1' ? 1 : 0) : -1;
   const bool umma_ok = vec_ok && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales);
   const int umma_min_m = k * n >= (32LL << 20) ? 2 : 3;
+  // 2 <= M <= 8 on matrices below 32 M weights, K a multiple of 1024, x small enough for shared memory: the
+  // direct-load mma.sync kernel (K = 4096, N = 4096: 6.8 / 7.4 / 9.1 us at M = 2 / 4 / 8 against 7.4 (SIMT) / 10.6 /
+  // 10.8 (tcgen05); at N = 14336 the legacy HMMA pipe makes it lose, 19.5 - 23.8 against 16.1 - 16.9, and at M = 1
+  // the SIMT kernel is as fast).  XDK_W4A16_MMA=0 leaves these shapes to the kernels below (comparison runs).
+  static const bool mma_env = !(getenv("XDK_W4A16_MMA") && getenv("XDK_W4A16_MMA")[0] == '0');
+  if (mma_env && plain && vec_ok && m >= 2 && m <= 8 && k % 1024 == 0 && k * n < (32LL << 20) &&
+      static_cast<size_t>(m) * (static_cast<size_t>(k) * 2 + 16) <= 160 * 1024)
+    return launch_mma(a, s);
   if (umma_ok && ((umma_env != 0 && m >= umma_min_m) || !plain)) {
     const int st = launch_umma(a, dependent, s);
     if (st != XDK_ERR_LIMIT || !plain) return st;

@@ -60,6 +60,22 @@ def test_baseline_shapes(m, n):
     assert y2 is out and torch.equal(y2, y)
 
 
+@pytest.mark.parametrize("m,k,n,group", [(2, 4096, 4096, 128), (5, 4096, 6144, 64), (8, 4096, 1000, 128), (3, 14336, 520, 128),
+                                         (8, 2048, 4100, 32)])
+def test_direct_load_tensor_core_kernel(m, k, n, group):
+    """2 <= M <= 8, K % 1024 == 0, below 32 M weights: 16 weight columns are the rows of mma.m16n8k16 tiles, the rows
+    of x its columns; eight warps split K.  Ragged N, several rounds of loads (K = 14336), bias, all groups."""
+    from cross_dsl_kernels_b200.w4a16 import w4a16_linear
+    x, packed, scales, b = make(m, k, n, group, True, seed=m + n)
+    y = w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), b.cuda(), group_size=group)
+    gate(y, x, packed, scales, b, group)
+    assert torch.equal(y, w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), b.cuda(), group_size=group)), "deterministic"
+    # the same rows inside a taller batch give the same values (while the taller x still fits the kernel's shared memory)
+    tall = torch.cat([x, torch.randn(8 - m, k).half()]) if m < 8 and 8 * (2 * k + 16) <= 160 * 1024 else None
+    if tall is not None:
+        assert torch.equal(w4a16_linear(tall.cuda(), packed.cuda(), scales.cuda(), b.cuda(), group_size=group)[:m], y)
+
+
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 9, 16])
 @pytest.mark.parametrize("group", [32, 64, 128, 256])
 def test_every_m_and_group(m, group):
