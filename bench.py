@@ -524,9 +524,15 @@ def main() -> None:
         # is short.  At N > 1 the step graph synchronises the ranks, so every rank must replay it the same number of
         # times: the count comes from the slowest rank's measured step time, never from a rank's own wall clock.
         extra = lockstep_replays(statistics.median(block_ms), args.steps)
-        for _ in range(extra):
-            graph.replay()
-        torch.cuda.synchronize()
+        for round_ in range(6):  # nvidia-smi can take seconds to start on a box with many GPUs: at most ~6 s of load
+            for _ in range(extra):
+                graph.replay()
+            torch.cuda.synchronize()
+            seen = torch.tensor([len(sampler.rows)], device="cuda")
+            if world > 1:
+                dist.all_reduce(seen, op=dist.ReduceOp.MIN)  # the same decision on every rank
+            if int(seen.item()) >= 3:
+                break
     mark("sweep timed")
     per_block = torch.tensor(block_ms, device="cuda", dtype=torch.float64)
     if world > 1:
