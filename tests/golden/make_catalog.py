@@ -17,7 +17,10 @@ import sys
 
 
 def main() -> int:
-    checkout = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        print(__doc__, file=sys.stderr)
+        return 2
+    checkout = pathlib.Path(sys.argv[1])
     shapes = checkout / "benchmarks" / "shapes"
     fp32 = json.loads((shapes / "comparison.json").read_text())["cases"]
     w4 = json.loads((shapes / "w4a16.json").read_text())["cases"]
