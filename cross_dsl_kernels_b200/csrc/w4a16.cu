@@ -8,16 +8,15 @@
 // FP16 rounding -- bit-identical to the format's definition half(float(q) * float(scale)), since
 // that FP32 product is exact.  Products with x accumulate in FP32.
 //
-// Compute paths (they share the unpack):
-//   * M <= 2: SIMT.  Lanes stride over the packed row, weights feed mixed-precision FMAs
-//     (FP16 operands, FP32 accumulator) and a warp shuffle finishes each column.
-//   * 3 <= M <= 16: tensor cores.  The op is then a real [16 x K] x [K x N] contraction: x is padded to
-//     16 rows and the dequantised weights go straight from registers into mma.m16n8k16 B fragments
-//     (FP32 accumulators).  The k order inside a fragment is free as long as A uses the same order, so
-//     x is stored in shared memory pre-permuted to the order the unpack produces and no weight ever
-//     moves between lanes.
-// Split-K slices of one column strip form a thread-block cluster and are summed in slice order
-// through distributed shared memory (one launch, no scratch, deterministic).
+// Compute paths (they share the unpack; the dispatcher at the end of the file picks one):
+//   * M <= 8, K % 1024 == 0: mma.m16n8k16 with the operands swapped -- 16 weight columns are the MMA's rows, the rows of
+//     x its columns -- fed from direct 16-byte loads (w4a16_mma_kernel).
+//   * M >= 9 (and any M with a strided or multi-rank output), K % 256 == 0, group >= 64: tcgen05 kind::f16 with the
+//     dequantised weights in tensor memory (w4a16_umma_kernel).
+//   * shapes those two decline: a TMA-fed mma.sync stream kernel (M >= 3, K % 128 == 0), a SIMT kernel (lanes stride
+//     over the packed row, mixed-precision FMAs, warp shuffle per column) and a generic kernel for any K.
+// The k order inside an MMA fragment is free as long as both operands use the same order, so x is stored in shared
+// memory pre-permuted to the order the unpack produces and no weight ever moves between lanes.
 #include <cooperative_groups.h>
 #include <stdlib.h>
 
@@ -964,44 +963,62 @@ w4a16_generic_kernel(W4Args a) {
 // k = chunk + 32 q.  An MMA does not care which k a fragment slot stands for as long as A and B agree, so slot pairs
 // are simply "the pairs the unpack produces": word w of a vector gives A pairs (k0,k4) (k1,k5) for one MMA and
 // (k2,k6) (k3,k7) for the next, and the matching B pairs are one 16-byte read of x, which sits in shared memory
-// already permuted to (0,4,1,5,2,6,3,7) inside every 8 k.  (The legacy HMMA pipe of this part retires one
-// m16n8k16 per 32 cycles and sub-partition; with x as the 16-row operand -- 8 columns of W per MMA -- that pipe
-// alone took 12 us at N = 14336.)
-// A CTA is eight warps that split K eight ways over the same 16 columns (all loads of a warp's share go out before
-// the first is used: one trip to HBM per column pass) and add their partial sums in shared memory in warp order.
-__global__ void __launch_bounds__(kThreads)
-w4a16_mma_kernel(W4Args a, int passes) {
+// already permuted to (0,4,1,5,2,6,3,7) inside every 8 k.  The legacy HMMA pipe of this part retires one m16n8k16
+// per 32 cycles and sub-partition (6.3 us for K = 4096, N = 14336 in this form; with x as the 16-row operand it
+// would be twice that), so the rest of the instruction stream has to fit beside it: 26 warp instructions per MMA
+// are left (13 of them the exact unpack), after taking everything out of the loop that does not depend on the
+// codes -- no zero-filling of registers for columns past N or rows past M (they read a valid column or row and
+// feed outputs that are never stored), scales widened to half2 when they are fetched, one base pointer per column.
+// The grid is one wave (as many CTAs as are resident at once), the groups of 16 columns dealt evenly.
+// A CTA is eight warps that split K eight ways over the same 16 columns and add their partial sums in shared
+// memory in warp order.  A warp's work is a sequence of batches (a column pass x a round of up to four 128-k chunks
+// of its K share); the loads of the next batch are in flight while the current one is unpacked and multiplied, in
+// two register buffers, so the weight stream never waits for the tensor pipe nor the pipe for the stream.
+struct MmaBatch {
+  U4 wv[4][2];      // [chunk][column n, column n + 8]: 32 codes each
+  __half2 sc[4][2]; // their scale, in both halves
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+w4a16_mma_kernel(W4Args a, int col_groups) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int pitch = a.k * 2 + 16;                          // bytes per x row: the pad puts the 8 rows on different banks
   unsigned char* xs = smem_raw;                            // [m rows][pitch], k permuted inside every 8
-  float* red = reinterpret_cast<float*>(smem_raw + ((static_cast<size_t>(a.m) * pitch + 127) & ~static_cast<size_t>(127)));  // [8 warps][32 lanes][4]
+  float* red = reinterpret_cast<float*>(smem_raw + ((static_cast<size_t>(a.m) * pitch + 127) & ~static_cast<size_t>(127)));  // [2][8 warps][32 lanes][4]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n = lane >> 2, q = lane & 3;
   const int row_bytes = a.k / 2;
   const int k_warp = a.k / kWarps;          // this warp's share of K, a multiple of 128
   const int chunks = k_warp / 128;          // 128 k per chunk: 32 per lane of a quad
+  constexpr int kBatchChunks = 4;
+  const int rounds = (chunks + kBatchChunks - 1) / kBatchChunks;
   const int k0 = warp * k_warp + q * 32;    // first k of this lane's vectors
-  const int cta_col0 = blockIdx.x * passes * 16;
+  // the groups of 16 columns are dealt evenly to the CTAs of the grid (all resident at once: no second wave)
+  const int group0 = static_cast<int>(static_cast<int64_t>(blockIdx.x) * col_groups / gridDim.x);
+  const int my_passes = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * col_groups / gridDim.x) - group0;  // >= 1
+  const int cta_col0 = group0 * 16;
 
-  // the first pass's weights go out before x is staged
-  constexpr int kMaxChunks = 4;             // chunks per round of loads (K <= 4096: one round)
-  U4 wv[kMaxChunks][2];                     // [chunk][column n, column n + 8]
-  __half sc[kMaxChunks][2];
-  auto fetch = [&](int col_base, int chunk0) {
+  const int scale_shift = 31 - __clz(a.group);  // group sizes are powers of two
+  // Columns past N (the last pass of the last CTA when N % 16 != 0) read the last column instead and chunks past the
+  // warp's share are not loaded at all: what they would feed is never stored, respectively never computed.
+  auto fetch = [&](MmaBatch& b, int col_base, int chunk0) {
 #pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c)
+    for (int h = 0; h < 2; ++h) {
+      const int col = min(col_base + h * 8 + n, a.n - 1), k = k0 + chunk0 * 128;
+      const uint8_t* wp = a.packed + static_cast<size_t>(col) * row_bytes + k / 2;
+      const __half* sp = a.scales + static_cast<size_t>(col) * a.groups;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int col = col_base + h * 8 + n, k = k0 + (chunk0 + c) * 128;
-        wv[c][h] = U4{0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};  // code 8 == weight 0
-        sc[c][h] = __float2half(0.0f);
-        if (chunk0 + c < chunks && col < a.n) {
-          wv[c][h] = ld_stream16(a.packed + static_cast<size_t>(col) * row_bytes + k / 2);
-          sc[c][h] = __ldg(a.scales + static_cast<size_t>(col) * a.groups + k / a.group);
+      for (int c = 0; c < kBatchChunks; ++c)
+        if (chunk0 + c < chunks) {
+          b.wv[c][h] = ld_stream16(wp + c * 64);
+          b.sc[c][h] = __half2half2(__ldg(sp + ((k + c * 128) >> scale_shift)));
         }
-      }
+    }
   };
-  fetch(cta_col0, 0);
+  MmaBatch buf0, buf1;
+  pdl_launch_dependents();
+  fetch(buf0, cta_col0, 0);  // the first batch's weights go out before x is staged
+  pdl_wait();                // x may be the preceding kernel's output; the weights are not
 
   const int units = a.k / 8;
   for (int i = threadIdx.x; i < a.m * units; i += kThreads) {
@@ -1015,70 +1032,88 @@ w4a16_mma_kernel(W4Args a, int passes) {
     *reinterpret_cast<U4*>(xs + static_cast<size_t>(r) * pitch + u * 16) = o;
   }
   __syncthreads();
-  const bool row_live = n < a.m;  // this lane's B fragments: row n of x
-  const unsigned char* xrow = xs + static_cast<size_t>(row_live ? n : 0) * pitch;
+  // this lane's B fragments: row n of x; lanes past M read row 0 and feed output rows that are never stored
+  const unsigned char* xrow = xs + static_cast<size_t>(n < a.m ? n : 0) * pitch;
 
-  for (int pass = 0; pass < passes; ++pass) {
-    const int col_base = cta_col0 + pass * 16;
-    if (col_base >= a.n) break;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // (column n, rows 2 q + {0, 1} of x), (column n + 8, the same rows)
-    for (int chunk0 = 0; chunk0 < chunks; chunk0 += kMaxChunks) {
-      if (chunk0 > 0) fetch(col_base, chunk0);
+  // two accumulator sets (the two MMAs of a word alternate, halving the dependent chain), summed at the end of a pass:
+  // (column n, rows 2 q + {0, 1} of x), (column n + 8, the same rows)
+  float acc0[4], acc1[4];
+  int pass = 0, round = 0;  // of the batch being computed
+  auto step = [&](MmaBatch& cur, MmaBatch& nxt) -> bool {
+    int np = pass, nr = round + 1;
+    if (nr == rounds) nr = 0, ++np;
+    const bool has_next = np < my_passes;
+    if (has_next) fetch(nxt, cta_col0 + np * 16, nr * kBatchChunks);
+    if (round == 0) {
 #pragma unroll
-      for (int c = 0; c < kMaxChunks; ++c) {
-        if (chunk0 + c < chunks) {
-          const unsigned char* xk = xrow + (k0 + (chunk0 + c) * 128) * 2;
+      for (int e = 0; e < 4; ++e) acc0[e] = acc1[e] = 0.0f;
+    }
+    const int chunk0 = round * kBatchChunks;
 #pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            U4 xv = U4{0u, 0u, 0u, 0u};
-            if (row_live) xv = *reinterpret_cast<const U4*>(xk + w * 16);
-            const uint32_t w0 = w == 0 ? wv[c][0].x : (w == 1 ? wv[c][0].y : (w == 2 ? wv[c][0].z : wv[c][0].w));
-            const uint32_t w1 = w == 0 ? wv[c][1].x : (w == 1 ? wv[c][1].y : (w == 2 ? wv[c][1].z : wv[c][1].w));
-            __half2 h0[4], h1[4];
-            dequant8(w0, __half2half2(sc[c][0]), h0);
-            dequant8(w1, __half2half2(sc[c][1]), h1);
-            mma16816(acc, *reinterpret_cast<uint32_t*>(&h0[0]), *reinterpret_cast<uint32_t*>(&h1[0]), *reinterpret_cast<uint32_t*>(&h0[1]),
-                     *reinterpret_cast<uint32_t*>(&h1[1]), xv.x, xv.y);
-            mma16816(acc, *reinterpret_cast<uint32_t*>(&h0[2]), *reinterpret_cast<uint32_t*>(&h1[2]), *reinterpret_cast<uint32_t*>(&h0[3]),
-                     *reinterpret_cast<uint32_t*>(&h1[3]), xv.z, xv.w);
-          }
+    for (int c = 0; c < kBatchChunks; ++c) {
+      if (chunk0 + c < chunks) {
+        const unsigned char* xk = xrow + (k0 + (chunk0 + c) * 128) * 2;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const U4 xv = *reinterpret_cast<const U4*>(xk + w * 16);
+          const uint32_t w0 = w == 0 ? cur.wv[c][0].x : (w == 1 ? cur.wv[c][0].y : (w == 2 ? cur.wv[c][0].z : cur.wv[c][0].w));
+          const uint32_t w1 = w == 0 ? cur.wv[c][1].x : (w == 1 ? cur.wv[c][1].y : (w == 2 ? cur.wv[c][1].z : cur.wv[c][1].w));
+          __half2 h0[4], h1[4];
+          dequant8(w0, cur.sc[c][0], h0);
+          dequant8(w1, cur.sc[c][1], h1);
+          mma16816(acc0, *reinterpret_cast<uint32_t*>(&h0[0]), *reinterpret_cast<uint32_t*>(&h1[0]), *reinterpret_cast<uint32_t*>(&h0[1]),
+                   *reinterpret_cast<uint32_t*>(&h1[1]), xv.x, xv.y);
+          mma16816(acc1, *reinterpret_cast<uint32_t*>(&h0[2]), *reinterpret_cast<uint32_t*>(&h1[2]), *reinterpret_cast<uint32_t*>(&h0[3]),
+                   *reinterpret_cast<uint32_t*>(&h1[3]), xv.z, xv.w);
         }
       }
     }
-    // the next pass's first round of weights is on its way while the partial sums meet
-    if (pass + 1 < passes && col_base + 16 < a.n) fetch(col_base + 16, 0);
-    *reinterpret_cast<float4*>(red + (warp * 32 + lane) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    __syncthreads();
-    if (warp == 0) {  // the eight partial sums in warp order, bias, store
-      float4 total = *reinterpret_cast<const float4*>(red + lane * 4);
-      for (int w = 1; w < kWarps; ++w) {
-        const float4 part = *reinterpret_cast<const float4*>(red + (w * 32 + lane) * 4);
-        total.x = __fadd_rn(total.x, part.x), total.y = __fadd_rn(total.y, part.y);
-        total.z = __fadd_rn(total.z, part.z), total.w = __fadd_rn(total.w, part.w);
-      }
-      const float out[4] = {total.x, total.y, total.z, total.w};
+    if (round == rounds - 1) {
+      // the partial sums of the pass meet in shared memory; the buffer alternates between passes, so one barrier
+      // per pass is enough (the warp that adds pass p has passed the barrier of pass p + 1 before anybody writes
+      // the buffer of pass p + 2), and the adding warp rotates
+      float* mine = red + (pass & 1) * (kWarps * 32 * 4);
+      *reinterpret_cast<float4*>(mine + (warp * 32 + lane) * 4) =
+          make_float4(__fadd_rn(acc0[0], acc1[0]), __fadd_rn(acc0[1], acc1[1]), __fadd_rn(acc0[2], acc1[2]), __fadd_rn(acc0[3], acc1[3]));
+      __syncthreads();
+      if (warp == (pass & (kWarps - 1))) {  // the eight partial sums in warp order, bias, store
+        const int col_base = cta_col0 + pass * 16;
+        float4 total = *reinterpret_cast<const float4*>(mine + lane * 4);
+        for (int w = 1; w < kWarps; ++w) {
+          const float4 part = *reinterpret_cast<const float4*>(mine + (w * 32 + lane) * 4);
+          total.x = __fadd_rn(total.x, part.x), total.y = __fadd_rn(total.y, part.y);
+          total.z = __fadd_rn(total.z, part.z), total.w = __fadd_rn(total.w, part.w);
+        }
+        const float out[4] = {total.x, total.y, total.z, total.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = col_base + (e >> 1) * 8 + n, row = q * 2 + (e & 1);
-        if (row < a.m && col < a.n)
-          a.y[static_cast<size_t>(row) * a.n + col] = __float2half_rn(out[e] + (a.bias ? __half2float(a.bias[col]) : 0.0f));
+        for (int e = 0; e < 4; ++e) {
+          const int col = col_base + (e >> 1) * 8 + n, row = q * 2 + (e & 1);
+          if (row < a.m && col < a.n)
+            a.y[static_cast<size_t>(row) * a.n + col] = __float2half_rn(out[e] + (a.bias ? __half2float(a.bias[col]) : 0.0f));
+        }
       }
     }
-    __syncthreads();  // red is free for the next pass
+    pass = np, round = nr;
+    return has_next;
+  };
+  while (step(buf0, buf1) && step(buf1, buf0)) {
   }
 }
 
-int launch_mma(W4Args a, cudaStream_t stream) {
+int launch_mma(W4Args a, bool dependent, cudaStream_t stream) {
   const size_t xbytes = (static_cast<size_t>(a.m) * (a.k * 2 + 16) + 127) & ~static_cast<size_t>(127);
-  const size_t smem = xbytes + static_cast<size_t>(kWarps) * 32 * 4 * sizeof(float);
+  const size_t smem = xbytes + 2 * static_cast<size_t>(kWarps) * 32 * 4 * sizeof(float);
   cudaError_t err = cudaFuncSetAttribute(w4a16_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (err != cudaSuccess) return note_launch(err);
-  // columns per CTA: enough CTAs for two per SM, at least one pass of 16 columns
+  // one wave: as many CTAs as the device holds at once (two per SM unless x takes more than half the shared memory);
+  // a grid of a few CTAs more than that ran as two waves and took twice the time
+  int resident = 0;
+  err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, w4a16_mma_kernel, kThreads, smem);
+  if (err != cudaSuccess) return note_launch(err);
+  if (resident < 1) return XDK_ERR_LIMIT;
   const int groups = (a.n + 15) / 16;
-  int passes = groups / (2 * sm_count());
-  if (passes < 1) passes = 1;
-  const int ctas = (groups + passes - 1) / passes;
-  return launch(w4a16_mma_kernel, dim3(ctas), dim3(kThreads), smem, stream, 1u, a, passes);
+  const int ctas = groups < resident * sm_count() ? groups : resident * sm_count();
+  return launch_opts(w4a16_mma_kernel, dim3(ctas), dim3(kThreads), smem, stream, 1u, dependent, a, groups);
 }
 
 template <int MT, int CW>
@@ -1150,22 +1185,22 @@ extern "C" int xdk_w4a16_peer(const void* x, const uint8_t* packed, const void* 
   const bool dependent = (flags & XDK_DEPENDENT_LAUNCH) != 0;
   a.out = out;
   const bool vec_ok = k % 32 == 0 && aligned16(packed) && aligned16(x);  // 16-byte vectors of 32 codes
-  // M >= 3 (M = 2 on large matrices), and every M whose output is strided or goes to several ranks: the tcgen05
-  // kernel.  Its time hardly depends on M (K = 4096, N = 14336: 17.1 us at M = 1, 17.6 at M = 8, 18.2 at M = 16),
-  // so it beats the mma.sync kernel from M = 3 on (24.9 us at M = 4, 25.3 at M = 8; N = 4096: 10.3 vs 10.7 and
-  // 10.5 vs 11.3) and the SIMT kernel at M = 2 on large matrices (17.2 vs 20.6 us; N = 4096: 10.2 vs 7.4, SIMT
-  // stays).  XDK_W4A16_UMMA=0 keeps it for strided and multi-rank outputs only (comparison runs).
+  // M <= 8 with K a multiple of 1024 and x small enough for shared memory: the direct-load mma.sync kernel
+  // (K = 4096: N = 4096 5.9 / 6.0 / 6.4 / 7.2 us at M = 1 / 2 / 4 / 8, N = 14336 14.7 / 14.8 / 15.3 / 16.1, N = 28672
+  // 23.3 - 24.9; K = 14336, N = 4096: 13.9 / 14.6 / 19.9 at M = 1 / 2 / 4 -- against 6.4 / 16.3 / 30.1 / 17.3 at M = 1
+  // for the SIMT kernel and 10.2 - 10.8 / 16.6 - 17.0 / 28.5 - 29.2 / 21.5 - 25.8 for the tcgen05 kernel).
+  // XDK_W4A16_MMA=0 leaves these shapes to the kernels below (comparison runs).
+  static const bool mma_env = !(getenv("XDK_W4A16_MMA") && getenv("XDK_W4A16_MMA")[0] == '0');
+  if (mma_env && plain && vec_ok && m <= 8 && k % 1024 == 0 &&
+      static_cast<size_t>(m) * (static_cast<size_t>(k) * 2 + 16) <= 160 * 1024)
+    return launch_mma(a, dependent, s);
+  // M >= 9, smaller M where the kernel above does not apply (M >= 3, M = 2 on large matrices), and every M whose
+  // output is strided or goes to several ranks: the tcgen05 kernel.  Its time hardly depends on M (K = 4096,
+  // N = 14336: 17.1 us at M = 1, 17.6 at M = 8, 18.2 at M = 16).  XDK_W4A16_UMMA=0 keeps it for strided and
+  // multi-rank outputs only (comparison runs).
   static const int umma_env = getenv("XDK_W4A16_UMMA") ? (getenv("XDK_W4A16_UMMA")[0] == '1' ? 1 : 0) : -1;
   const bool umma_ok = vec_ok && k % 256 == 0 && group_size >= 64 && a.groups <= 256 && a.groups % 8 == 0 && aligned16(scales);
   const int umma_min_m = k * n >= (32LL << 20) ? 2 : 3;
-  // 2 <= M <= 8 on matrices below 32 M weights, K a multiple of 1024, x small enough for shared memory: the
-  // direct-load mma.sync kernel (K = 4096, N = 4096: 6.8 / 7.4 / 9.1 us at M = 2 / 4 / 8 against 7.4 (SIMT) / 10.6 /
-  // 10.8 (tcgen05); at N = 14336 the legacy HMMA pipe makes it lose, 19.5 - 23.8 against 16.1 - 16.9, and at M = 1
-  // the SIMT kernel is as fast).  XDK_W4A16_MMA=0 leaves these shapes to the kernels below (comparison runs).
-  static const bool mma_env = !(getenv("XDK_W4A16_MMA") && getenv("XDK_W4A16_MMA")[0] == '0');
-  if (mma_env && plain && vec_ok && m >= 2 && m <= 8 && k % 1024 == 0 && k * n < (32LL << 20) &&
-      static_cast<size_t>(m) * (static_cast<size_t>(k) * 2 + 16) <= 160 * 1024)
-    return launch_mma(a, s);
   if (umma_ok && ((umma_env != 0 && m >= umma_min_m) || !plain)) {
     const int st = launch_umma(a, dependent, s);
     if (st != XDK_ERR_LIMIT || !plain) return st;

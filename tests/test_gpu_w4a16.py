@@ -61,10 +61,13 @@ def test_baseline_shapes(m, n):
 
 
 @pytest.mark.parametrize("m,k,n,group", [(2, 4096, 4096, 128), (5, 4096, 6144, 64), (8, 4096, 1000, 128), (3, 14336, 520, 128),
-                                         (8, 2048, 4100, 32)])
+                                         (8, 2048, 4100, 32), (1, 4096, 14336, 128), (1, 1024, 24, 256), (4, 4096, 28672 + 8, 128),
+                                         (5, 14336, 4096, 128), (7, 3072, 4752 * 2, 64)])
 def test_direct_load_tensor_core_kernel(m, k, n, group):
-    """2 <= M <= 8, K % 1024 == 0, below 32 M weights: 16 weight columns are the rows of mma.m16n8k16 tiles, the rows
-    of x its columns; eight warps split K.  Ragged N, several rounds of loads (K = 14336), bias, all groups."""
+    """M <= 8, K % 1024 == 0: 16 weight columns are the rows of mma.m16n8k16 tiles, the rows of x its columns; eight
+    warps split K and walk double-buffered batches.  Ragged N (a last pass that reads clamped columns), more column
+    groups than resident CTAs (several passes per CTA), several rounds of loads per pass (K = 14336, with a last
+    round of two chunks; K = 3072 with three), one CTA per SM when x is large, bias, all groups."""
     from cross_dsl_kernels_b200.w4a16 import w4a16_linear
     x, packed, scales, b = make(m, k, n, group, True, seed=m + n)
     y = w4a16_linear(x.cuda(), packed.cuda(), scales.cuda(), b.cuda(), group_size=group)
