@@ -753,12 +753,13 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
         if (ok) ok = mbar_wait(x_empty + xb, xs.parity ^ 1u);  // a fresh barrier passes: nothing has read the buffer yet
         xs.advance(xdepth);
         if (ok) {
-          for (int ks = 0; ks < cur.split; ++ks) {
+          auto fetch = [&](int ks, U4 (&v)[8]) {
             const unsigned char* src = xraw + xb * xstride + ks * 16 * kUStepK * 2 + kg * 16;
-            unsigned char* dst = xbuf + xb * xstride + (ks * 2 + mg) * kUXSbo + kg * kUXLbo;
-            U4 v[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r) v[r] = *reinterpret_cast<const U4*>(src + (mg * 8 + ((li + r) & 7)) * (kUStepK * 2));
+          };
+          auto place = [&](int ks, const U4 (&v)[8]) {
+            unsigned char* dst = xbuf + xb * xstride + (ks * 2 + mg) * kUXSbo + kg * kUXLbo;
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
               U4 o;  // k 0..7 of one row -> 0,4,1,5,2,6,3,7, the order the unpack produces
@@ -767,6 +768,21 @@ w4a16_umma_kernel(W4Args a, UmmaPlan plan, const __grid_constant__ CUtensorMap w
               o.z = __byte_perm(v[r].y, v[r].w, 0x5410);
               o.w = __byte_perm(v[r].y, v[r].w, 0x7632);
               *reinterpret_cast<U4*>(dst + ((li + r) & 7) * 16) = o;
+            }
+          };
+          if (cur.split == 1) {
+            U4 v[8];
+            fetch(0, v);
+            place(0, v);
+          } else {
+            // a step of a strip that splits K carries 2 or 4 k ranges of x: two at a time, so that the two x warps
+            // have sixteen loads in flight instead of eight (the x path sets the step time of these strips)
+            for (int ks = 0; ks < cur.split; ks += 2) {
+              U4 va[8], vb[8];
+              fetch(ks, va);
+              fetch(ks + 1, vb);
+              place(ks, va);
+              place(ks + 1, vb);
             }
           }
           fence_async_smem();
