@@ -758,11 +758,13 @@ extern "C" int xdk_gemv_f32_peer(const float* x, const float* w, const float* bi
   const int64_t strips_wide = (n + bn_wide - 1) / bn_wide;
   int splits = split_k;
   if (splits == 0) {
-    // Smallest split that puts about 1.5 CTAs on every SM (2.7 for the light M <= 2 KN kernel), as long
-    // as the whole grid is resident at once: a second wave costs more than any split gains.
-    const int ctas_per_sm = mt <= 2 ? 4 : (mt <= 4 ? 3 : 2);  // register-limited residency of the MT variants
+    // Smallest split that puts about 1.5 CTAs on every SM (2.7 for the KN kernels of M <= 4, whose 128-column strips
+    // are few: K = 4096, N = 14336, M = 4 took 44.6 us with 224 CTAs and 40.9 with 448), as long as the whole grid is
+    // resident at once: a second wave costs more than any split gains.
+    const bool vec = aligned16(w) && aligned16(x) && k % 4 == 0 && (nk ? true : n % 4 == 0);
+    const int ctas_per_sm = mt <= 2 ? 4 : (mt <= 4 ? (vec ? 4 : 3) : 2);  // register-limited residency of the MT variants
     const int64_t slots = static_cast<int64_t>(sm_count()) * ctas_per_sm;
-    const int64_t want = (!nk && mt <= 2) ? 400 : 222;
+    const int64_t want = (!nk && mt <= 4) ? 400 : 222;
     splits = 1;
     while (splits < 8 && strips_wide * splits < want && strips_wide * splits * 2 <= slots && k / (splits * 2) >= 256)
       splits *= 2;
