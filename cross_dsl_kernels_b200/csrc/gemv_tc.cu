@@ -401,9 +401,22 @@ gemv_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_
                 split_tf32(v.w, hi[4 * p + 3], lo[4 * p + 3]);
               }
             } else {
+              // the tile's row pitch follows the strip's width; one copy of the sixteen loads per width, so that their
+              // offsets are immediates instead of an address computation per load
               const uint32_t* colp = reinterpret_cast<const uint32_t*>(tile) + (kh * (kStepK / 2) + g * 16) * pitch + uq * 32 + lane;
+              if (pitch == 96) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) split_tf32(colp[j * pitch], hi[j], lo[j]);
+                for (int j = 0; j < 16; ++j) split_tf32(colp[j * 96], hi[j], lo[j]);
+              } else if (pitch == 128) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) split_tf32(colp[j * 128], hi[j], lo[j]);
+              } else if (pitch == 32) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) split_tf32(colp[j * 32], hi[j], lo[j]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) split_tf32(colp[j * 64], hi[j], lo[j]);
+              }
             }
             tmem_st16(a_lane_base + s * kStageCols + g * 16, hi);
             tmem_st16(a_lane_base + s * kStageCols + kStepK + g * 16, lo);
